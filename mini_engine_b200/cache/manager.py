@@ -51,6 +51,7 @@ class GroupSpec:
     window: int | None = None  # None: every key is kept
     num_blocks: int | None = None
     shareable: bool = True
+    keep_first: int = 0  # with a window: the first tokens of a sequence stay readable, their pages are never given back
 
 
 @dataclass(frozen=True)
@@ -202,10 +203,20 @@ class CacheManager:
     def _first_needed_page(self, group: GroupSpec, num_computed: int) -> int:
         """Pages below this index are behind the group's window once ``num_computed`` tokens
         are in the cache: the next query, at position ``num_computed``, reads keys at
-        positions ``> num_computed - window``."""
+        positions ``> num_computed - window``.  (The pages of a group's kept first tokens lie below
+        it too and are needed all the same: see :meth:`_kept_pages`.)"""
         if group.window is None:
             return 0
         return max(0, num_computed - group.window + 1) // self.block_size
+
+    def _kept_pages(self, group: GroupSpec) -> int:
+        """Pages at the start of a sequence that a group with a window never gives back."""
+        if group.window is None or group.keep_first <= 0:
+            return 0
+        return -(-group.keep_first // self.block_size)
+
+    def _page_needed(self, group: GroupSpec, index: int, num_computed: int) -> bool:
+        return index >= self._first_needed_page(group, num_computed) or index < self._kept_pages(group)
 
     def match_prefix(self, token_ids: Seq[int]) -> list[list[int]]:
         """Per group, the block table of the longest prefix of ``token_ids`` that the cache still
@@ -232,14 +243,13 @@ class CacheManager:
                 break
             length = i + 1
             if all(
-                None not in pages[self._first_needed_page(group, length * bs) : length]
+                all(pages[i] is not None for i in range(length) if self._page_needed(group, i, length * bs))
                 for group, pages in zip(self.groups, found)
             ):
                 best = length
         hits: list[list[int]] = []
         for group, pages in zip(self.groups, found):
-            first = self._first_needed_page(group, best * bs)
-            hits.append([NULL_PAGE if i < first else pages[i] for i in range(best)])
+            hits.append([pages[i] if self._page_needed(group, i, best * bs) else NULL_PAGE for i in range(best)])
         return hits
 
     # ---------------------------------------------------------------- mutations
@@ -281,7 +291,7 @@ class CacheManager:
         entries become ``NULL_PAGE``.  Returns how many pages were given back."""
         count = 0
         for group, pool, table in zip(self.groups, self.pools, req.block_tables):
-            for i in range(min(self._first_needed_page(group, num_computed), len(table))):
+            for i in range(self._kept_pages(group), min(self._first_needed_page(group, num_computed), len(table))):
                 if table[i] != NULL_PAGE:
                     pool.release(table[i])
                     table[i] = NULL_PAGE

@@ -25,7 +25,7 @@ class CacheLayout:
     groups: list[GroupSpec]
     group_specs: list[PagedCacheSpec]
     views: list[LayerCache]  # one per execution entry
-    arrays: list[torch.Tensor]  # per group [entries, 2, pages + 1, kv_heads, block_size, head_dim]
+    arrays: list[torch.Tensor]  # per group [entries, 2, pages + 1, kv_heads, block_size, head_dim]; keys and values apart when their widths differ
     slot_groups: list[SlotGroupSpec]  # one per execution entry whose mixer keeps per-request state
     bytes_per_token: int
 
@@ -69,14 +69,19 @@ def pages_of_group(spec: PagedCacheSpec, num_blocks: int, block_size: int, max_n
     if spec.window is None:
         return num_blocks
     per_request = -(-(spec.window + max_step_tokens) // block_size) + 2
+    per_request += -(-spec.keep_first // block_size)  # the kept first tokens' pages stay for good
     return max(1, min(num_blocks, max_num_seqs * per_request))
 
 
 def group_names(specs: list[PagedCacheSpec], pages: list[int]) -> list[GroupSpec]:
     return [
-        GroupSpec(f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f":w{s.window}" if s.window else ""), s.window, count)
+        GroupSpec(
+            f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f"+{s.v_dim}" if s.v_dim != s.head_dim else "")
+            + (f":w{s.window}" if s.window else "") + (f":first{s.keep_first}" if s.window and s.keep_first else ""),
+            s.window, count, keep_first=s.keep_first if s.window else 0,
+        )
         for i, (s, count) in enumerate(zip(specs, pages))
-    ]
+    ]  # fmt: skip
 
 
 def bytes_per_token(
@@ -85,7 +90,7 @@ def bytes_per_token(
     """Bytes of keys and values that one token occupies over all order entries that own a cache."""
     element = torch.empty((), dtype=dtype).element_size()
     return sum(
-        2 * paged.kv_heads * paged.head_dim * element
+        paged.kv_heads * (paged.head_dim + paged.v_dim) * element
         for paged, _state, cache_of in needs
         if paged is not None and cache_of is None
     )
@@ -132,12 +137,18 @@ def allocate_cache(
         if paged is not None and cache_of is None:
             owners[group_of[entry]].append(entry)
     element = torch.empty((), dtype=dtype).element_size()
-    arrays = [
-        torch.zeros(
-            (len(entries), 2, count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device
-        )
-        for s, entries, count in zip(specs, owners, pages)
-    ]
+    # Keys and values of a group lie in one array when their heads are equally wide; else in two.
+    arrays, key_arrays, value_arrays = [], [], []
+    for s, entries, count in zip(specs, owners, pages):
+        if s.v_dim == s.head_dim:
+            both = torch.zeros((len(entries), 2, count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device)
+            arrays.append(both)
+            key_arrays.append(both[:, 0]), value_arrays.append(both[:, 1])
+        else:
+            keys = torch.zeros((len(entries), count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device)
+            values = torch.zeros((len(entries), count + 1, s.kv_heads, block_size, s.v_dim), dtype=dtype, device=device)
+            arrays += [keys, values]
+            key_arrays.append(keys), value_arrays.append(values)
     views: list[LayerCache] = []
     slot_groups: list[SlotGroupSpec] = []
     for entry, (paged, state, cache_of) in enumerate(needs):
@@ -146,11 +157,11 @@ def allocate_cache(
             g = group_of[entry]
             owner = entry if cache_of is None else cache_of
             index = owners[g].index(owner)
-            view.group, view.k, view.v = g, arrays[g][index, 0], arrays[g][index, 1]
+            view.group, view.k, view.v = g, key_arrays[g][index], value_arrays[g][index]
             view.writes = cache_of is None
         if state is not None:
             slot_groups.append(SlotGroupSpec(f"state{entry}:{'x'.join(map(str, state.shape))}"))
             view.state = torch.zeros((max_num_seqs + 1, *state.shape), dtype=state.dtype, device=device)
         views.append(view)
-    per_token = sum(2 * len(e) * s.kv_heads * s.head_dim * element for s, e in zip(specs, owners))
+    per_token = sum(len(e) * s.kv_heads * (s.head_dim + s.v_dim) * element for s, e in zip(specs, owners))
     return CacheLayout(group_names(specs, pages), specs, views, arrays, slot_groups, per_token)

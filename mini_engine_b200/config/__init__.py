@@ -2,6 +2,7 @@
 
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
+from mini_engine_b200.config.pimezen import PimezenConfig
 from mini_engine_b200.config.qwen3 import Qwen3Config
 from mini_engine_b200.config.registry import (
     Architecture,
@@ -18,6 +19,7 @@ __all__ = [
     "ModelSpec",
     "OrderEntry",
     "PartSpec",
+    "PimezenConfig",
     "Qwen3Config",
     "architecture_for",
     "load_model_config",

@@ -35,16 +35,20 @@ class LayerSpec:
     names that the block's class asks for to norm parts: a pre-norm block asks for ``"mixer"``
     and ``"feed_forward"`` (the norm in front of each); another arrangement may ask for more
     (norms behind the mixer and the feed-forward, say).  ``mixer_norm`` and
-    ``feed_forward_norm`` are those two entries under their old names.
+    ``feed_forward_norm`` are those two entries under their old names.  ``feed_forward`` is ``None``
+    for a layer that has none (its block must be one that runs without).  ``block_params`` are the
+    constants and tensor names of an arrangement that has some of its own (layer scales, say); the
+    block is then built as ``cls(mixer, feed_forward, norms, prefix=, hidden_size=, **block_params)``.
     """
 
     prefix: str
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     mixer_norm: PartSpec | None = None
     feed_forward_norm: PartSpec | None = None
     norms: Mapping[str, PartSpec] = field(default_factory=dict)
+    block_params: Mapping[str, Any] = field(default_factory=dict)
 
     def named_norms(self) -> dict[str, PartSpec]:
         """Every norm of the layer by the name its block knows it under."""

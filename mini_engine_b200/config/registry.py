@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``config.json: architectures[0]``) to its
+"""One registry from an architecture's name (``config.json: architectures[0]``, or ``architecture``) to its
 typed configuration and to the function that lays the model out as a :class:`ModelSpec`.
 
 The reference has no registry: it checks ``model_type`` and builds its only model
@@ -53,8 +53,10 @@ def architecture_of_folder(folder: str | Path) -> Architecture:
         raise FileNotFoundError(f"{folder} has no config.json")
     raw = json.loads(config_file.read_text())
     names = raw.get("architectures") or []
+    if isinstance(raw.get("architecture"), str):  # some designs name themselves with one string
+        names = [raw["architecture"], *names]
     if not names:
-        raise KeyError(f"{config_file} has no 'architectures' entry to choose a model by")
+        raise KeyError(f"{config_file} has neither an 'architectures' nor an 'architecture' entry to choose a model by")
     return architecture_for(names[0])
 
 

@@ -122,7 +122,7 @@ template <typename OutT, bool VEC, int LANES, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
                    const float* __restrict__ weight, float eps, OutT* __restrict__ out,
-                   const int* __restrict__ rows, int hidden) {
+                   const int* __restrict__ rows, int hidden, const float* __restrict__ pending_scale) {
     constexpr int PLAYED = LANES / THREADS;  // lanes per thread
     extern __shared__ float row_cache[];  // [hidden]
     __shared__ float warp_partial[LANES / 32];
@@ -151,9 +151,19 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
 #pragma unroll
                 for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
                     if (s < splits) part[s] = *reinterpret_cast<const float4*>(pending_row + s * split_stride + i);
+                if (pending_scale != nullptr && splits > 0) {
+                    // x + scale * (sum of the partial sums): the part's output is whole before it is scaled
+                    float4 sum = part[0];
 #pragma unroll
-                for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
-                    if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+                    for (int s = 1; s < MAX_UNROLLED_SPLITS; ++s)
+                        if (s < splits) { sum.x += part[s].x; sum.y += part[s].y; sum.z += part[s].z; sum.w += part[s].w; }
+                    const float4 c = *reinterpret_cast<const float4*>(pending_scale + i);
+                    v.x = fmaf(c.x, sum.x, v.x); v.y = fmaf(c.y, sum.y, v.y); v.z = fmaf(c.z, sum.z, v.z); v.w = fmaf(c.w, sum.w, v.w);
+                } else {
+#pragma unroll
+                    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+                        if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+                }
                 *reinterpret_cast<float4*>(row_cache + i) = v;
                 if (write_back) *reinterpret_cast<float4*>(x_row + i) = v;
                 sum_sq[k] = fmaf(v.x, v.x, sum_sq[k]);
@@ -169,7 +179,13 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
                 const int i = base + k * THREADS + threadIdx.x;
                 if (i >= hidden) continue;
                 float v = x_row[i];
-                for (int s = 0; s < splits; ++s) v += pending_row[s * split_stride + i];
+                if (pending_scale != nullptr && splits > 0) {
+                    float sum = pending_row[i];
+                    for (int s = 1; s < splits; ++s) sum += pending_row[s * split_stride + i];
+                    v = fmaf(pending_scale[i], sum, v);
+                } else {
+                    for (int s = 0; s < splits; ++s) v += pending_row[s * split_stride + i];
+                }
                 row_cache[i] = v;
                 if (write_back) x_row[i] = v;
                 sum_sq[k] = fmaf(v, v, sum_sq[k]);
@@ -202,12 +218,12 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
 template <typename OutT, bool VEC, int LANES, int THREADS>
 static int launch_add_rmsnorm_threads(float* x, const float* pending, int splits, size_t split_stride,
                                       const float* weight, float eps, OutT* out, const int* rows, int count, int hidden,
-                                      cudaStream_t stream) {
+                                      cudaStream_t stream, const float* pending_scale) {
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
     auto kernel = add_rmsnorm_kernel<OutT, VEC, LANES, THREADS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_kernel(kernel, count, THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
-                         rows, hidden);
+                         rows, hidden, pending_scale);
 }
 
 // Few rows: one lane per thread.  Many rows: 256 threads per row, more rows per SM.  The lanes
@@ -216,50 +232,54 @@ constexpr int NORM_MANY_ROWS = 256;
 
 template <typename OutT, bool VEC, int LANES>
 static int launch_add_rmsnorm_lanes(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
-                                    float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+                                    float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream,
+                                    const float* pending_scale) {
     if (count >= NORM_MANY_ROWS)
-        return launch_add_rmsnorm_threads<OutT, VEC, LANES, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
-    return launch_add_rmsnorm_threads<OutT, VEC, LANES, LANES>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+        return launch_add_rmsnorm_threads<OutT, VEC, LANES, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
+    return launch_add_rmsnorm_threads<OutT, VEC, LANES, LANES>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
 }
 
 template <typename OutT, bool VEC>
 static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
-                              float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+                              float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream,
+                                    const float* pending_scale) {
     if (VEC && hidden > 2048)
-        return launch_add_rmsnorm_lanes<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
     if (VEC && hidden > 1024)
-        return launch_add_rmsnorm_lanes<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
-    return launch_add_rmsnorm_lanes<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
+    return launch_add_rmsnorm_lanes<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long long split_stride,
                              const float* weight, float eps, void* out, int out_type, const int* rows,
-                             int count, int hidden, cudaStream_t stream) {
+                             int count, int hidden, const float* pending_scale, cudaStream_t stream) {
     if (count <= 0) return 0;
     if (static_cast<size_t>(hidden) * sizeof(float) > 200 * 1024) return ME_ERR_UNSUPPORTED;
     // Which path runs depends on the width and on the alignment of the engine's persistent
     // buffers only, never on the batch, so a row's statistics are the same bits in every step.
     const bool vec = hidden % 4 == 0 && aligned16(x) && aligned16(weight) && aligned16(out) &&
-                     (pending == nullptr || (aligned16(pending) && split_stride % 4 == 0));
+                     (pending == nullptr || (aligned16(pending) && split_stride % 4 == 0)) && aligned16(pending_scale);
     const size_t stride = static_cast<size_t>(split_stride);
     if (out_type == ME_BF16) {
         auto* o = static_cast<__nv_bfloat16*>(out);
-        return vec ? launch_add_rmsnorm<__nv_bfloat16, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream)
-                   : launch_add_rmsnorm<__nv_bfloat16, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream);
+        return vec ? launch_add_rmsnorm<__nv_bfloat16, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale)
+                   : launch_add_rmsnorm<__nv_bfloat16, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale);
     }
     auto* o = static_cast<float*>(out);
-    return vec ? launch_add_rmsnorm<float, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream)
-               : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream);
+    return vec ? launch_add_rmsnorm<float, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale)
+               : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale);
 }
 
 // --------------------------------------------------------------------------------- SwiGLU
 
-// partial[s][t][0..inter) are gate sums, [inter..2*inter) up sums.  out = silu(gate) * up.
+// partial[s][t][0..inter) are gate sums, [inter..2*inter) up sums.  out = g * sigmoid(slope * g) * (u + offset)
+// with g = min(gate, limit) and u = clamp(up, -limit, limit) when limit > 0, else g = gate and u = up;
+// slope 1, no limit and offset 0 are silu(gate) * up.
 template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
-                              OutT* __restrict__ out, int tokens, int inter) {
+                              OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset) {
     const size_t total = static_cast<size_t>(tokens) * inter;
     pdl_trigger();
     pdl_wait();
@@ -273,22 +293,26 @@ __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, siz
             gate += base[s * split_stride + i];
             up += base[s * split_stride + inter + i];
         }
-        const float activated = gate / (1.0f + expf(-gate));
-        out[idx] = from_float<OutT>(activated * up);
+        if (limit > 0.0f) {
+            gate = fminf(gate, limit);
+            up = fminf(fmaxf(up, -limit), limit);
+        }
+        const float activated = gate / (1.0f + expf(-slope * gate));
+        out[idx] = from_float<OutT>(activated * (up + offset));
     }
 }
 
 ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride, void* out, int out_type,
-                        int tokens, int inter, cudaStream_t stream) {
+                        int tokens, int inter, float slope, float limit, float offset, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const size_t total = static_cast<size_t>(tokens) * inter;
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
     if (out_type == ME_BF16)
         return launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, partial, splits,
-                             (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter);
+                             (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset);
     return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
-                         static_cast<float*>(out), tokens, inter);
+                         static_cast<float*>(out), tokens, inter, slope, limit, offset);
 }
 
 // ------------------------------------------------- per-head norm + rotary + cache write
@@ -317,6 +341,7 @@ struct QkvArgs {
     int tokens, heads, kv_heads, head_dim, page_size;
     int rotary_dim;  // the first rotary_dim elements of a head are rotated (in halves of rotary_dim / 2), the rest pass through
     const float* bias;  // [(heads + 2 kv_heads) * head_dim] added to the projections' sums, or null
+    int value_dim;      // width of a value head (head_dim in most models): the v columns are kv_heads * value_dim
 };
 
 constexpr int QKV_WARPS = 4;
@@ -331,23 +356,28 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     if (item >= static_cast<long long>(a.tokens) * heads_total) return;
     const int token = static_cast<int>(item / heads_total);
     const int column_head = static_cast<int>(item % heads_total);
-    const int d = a.head_dim, half = a.rotary_dim / 2;
-    float* vec = staged + warp * d;
+    const int half = a.rotary_dim / 2;
+    const bool is_q = column_head < a.heads;
+    const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
+    // Query and key heads are head_dim wide, value heads value_dim.
+    const int d = (is_q || is_k) ? a.head_dim : a.value_dim;
+    float* vec = staged + warp * max(a.head_dim, a.value_dim);
     pdl_trigger();
     pdl_wait();
 
-    const size_t row_width = static_cast<size_t>(heads_total) * d;
-    const float* src = a.qkv + static_cast<size_t>(token) * row_width + static_cast<size_t>(column_head) * d;
+    const size_t qk_heads = static_cast<size_t>(a.heads + a.kv_heads);
+    const size_t row_width = qk_heads * a.head_dim + static_cast<size_t>(a.kv_heads) * a.value_dim;
+    const size_t column = (is_q || is_k) ? static_cast<size_t>(column_head) * a.head_dim
+                                         : qk_heads * a.head_dim + (column_head - qk_heads) * a.value_dim;
+    const float* src = a.qkv + static_cast<size_t>(token) * row_width + column;
     float sum_sq = 0.0f;
     for (int i = lane; i < d; i += 32) {
         float v = 0.0f;
         for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
-        if (a.bias) v += a.bias[static_cast<size_t>(column_head) * d + i];
+        if (a.bias) v += a.bias[column + i];
         vec[i] = v;
         sum_sq = fmaf(v, v, sum_sq);
     }
-    const bool is_q = column_head < a.heads;
-    const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
     const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
     float inv = 1.0f;
     if (weight) {
@@ -498,17 +528,18 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
                                     const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
                                     void* v_pages, void* k_dense, void* v_dense, int out_type, int tokens,
                                     int heads, int kv_heads, int head_dim, int page_size, int rotary_dim,
-                                    const float* bias, cudaStream_t stream) {
+                                    const float* bias, int value_dim, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (head_dim > MAX_HEAD_DIM || head_dim % 2) return ME_ERR_UNSUPPORTED;
+    if (head_dim > MAX_HEAD_DIM || (head_dim % 2 && cos_sin != nullptr)) return ME_ERR_UNSUPPORTED;
+    if (value_dim < 1 || value_dim > MAX_HEAD_DIM) return ME_ERR_UNSUPPORTED;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
     QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin), positions, slot_mapping,
-              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size, rotary_dim, bias};
+              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size, rotary_dim, bias, value_dim};
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
-    const size_t smem = static_cast<size_t>(QKV_WARPS) * head_dim * sizeof(float);
+    const size_t smem = static_cast<size_t>(QKV_WARPS) * std::max(head_dim, value_dim) * sizeof(float);
     // The choice depends on the model's sizes and the engine's buffers only, never on the batch.
-    const bool vec = head_dim == 128 && rotary_dim == head_dim && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
+    const bool vec = head_dim == 128 && value_dim == 128 && rotary_dim == head_dim && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
                      aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin) && aligned16(bias);
     if (vec) {
@@ -560,4 +591,51 @@ ME_EXPORT int me_kv_store(const void* k_dense, const void* v_dense, const int* s
     return launch_kernel(kv_store_kernel<float>, tokens, 128, 0, stream, static_cast<const float*>(k_dense),
                          static_cast<const float*>(v_dense), slot_mapping, static_cast<float*>(k_pages),
                          static_cast<float*>(v_pages), kv_heads, head_dim, page_size);
+}
+
+// ------------------------------------------------------- weighted sum of parallel branches
+
+// out[t][c] = sum_b factor[b] * (sum_s partial_b[s][t][c]): the outputs of mixers that read the same
+// input side by side, each still in the partial sums of its last product, joined into one float32 array.
+constexpr int MAX_BRANCHES = 4;
+struct BranchArgs {
+    const float* partial[MAX_BRANCHES];
+    int splits[MAX_BRANCHES];
+    size_t split_stride[MAX_BRANCHES];
+    float factor[MAX_BRANCHES];
+    int branches;
+};
+
+__global__ void branch_sum_kernel(BranchArgs a, float* __restrict__ out, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float sum = 0.0f;
+        for (int b = 0; b < a.branches; ++b) {
+            float whole = 0.0f;
+            for (int s = 0; s < a.splits[b]; ++s) whole += a.partial[b][s * a.split_stride[b] + idx];
+            sum = fmaf(a.factor[b], whole, sum);
+        }
+        out[idx] = sum;
+    }
+}
+
+ME_EXPORT int me_branch_sum(const float* const* partials, const int* splits, const long long* strides,
+                            const float* factors, int branches, float* out, int tokens, int width,
+                            cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (branches < 1 || branches > MAX_BRANCHES) return ME_ERR_UNSUPPORTED;
+    BranchArgs a{};
+    a.branches = branches;
+    for (int b = 0; b < branches; ++b) {
+        a.partial[b] = partials[b];
+        a.splits[b] = splits[b];
+        a.split_stride[b] = static_cast<size_t>(strides[b]);
+        a.factor[b] = factors[b];
+    }
+    const size_t total = static_cast<size_t>(tokens) * width;
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+    return launch_kernel(branch_sum_kernel, blocks, threads, 0, stream, a, out, total);
 }

@@ -177,11 +177,13 @@ def add_rmsnorm(
     eps: float,
     out: torch.Tensor,
     rows: torch.Tensor | None = None,
+    pending_scale: torch.Tensor | None = None,
 ) -> None:
     """``x += sum_s pending[s]`` (in place, float32) and ``out = weight * rmsnorm(x)``.
 
     With ``rows`` only ``x[rows]`` (+ pending) are normalised into ``out[0..len(rows))`` and
-    ``x`` is not modified."""
+    ``x`` is not modified.  With ``pending_scale`` (float32 ``[hidden]``) the sum that is added is
+    ``pending_scale * sum_s pending[s]``, column by column."""
     _need(x, torch.float32, "x"), _need(weight, torch.float32, "weight"), _need(out, None, "out")
     hidden = x.shape[-1]
     splits, stride = 0, 0
@@ -195,27 +197,38 @@ def add_rmsnorm(
     count = x.shape[0] if rows is None else rows.shape[0]
     if rows is not None:
         _need(rows, torch.int32, "rows")
+    if pending_scale is not None:
+        _need(pending_scale, torch.float32, "pending_scale")
+        if pending_scale.shape != (hidden,):
+            raise KernelError("add_rmsnorm: pending_scale must have one value per column")
     fn = _fn(
         "elementwise",
         "me_add_rmsnorm",
-        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     )
     code = fn(
         _ptr(x), _ptr(pending), splits, stride, _ptr(weight), eps, _ptr(out), _type_code(out.dtype),
-        _ptr(rows), count, hidden, _stream(),
+        _ptr(rows), count, hidden, _ptr(pending_scale), _stream(),
     )  # fmt: skip
     _check(code, "add_rmsnorm")
 
 
-def swiglu(partials: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = silu(gate) * up`` where gate/up are the halves of ``sum_s partials[s]``."""
+def swiglu(
+    partials: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0
+) -> None:
+    """``out = g * sigmoid(slope * g) * (u + offset)`` where gate/up are the halves of ``sum_s
+    partials[s]``, ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)`` when a limit is
+    given, else ``g = gate``, ``u = up``.  The defaults are ``silu(gate) * up``."""
     _need(partials, torch.float32, "partials"), _need(out, None, "out")
     splits, tokens, width = partials.shape
     inter = width // 2
     if out.shape != (tokens, inter):
         raise KernelError(f"swiglu: out {tuple(out.shape)} does not fit partials {tuple(partials.shape)}")
-    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
-    code = fn(_ptr(partials), splits, partials.stride(0), _ptr(out), _type_code(out.dtype), tokens, inter, _stream())
+    if limit is not None and not limit > 0:
+        raise KernelError("the limit of a gated activation must be positive (or absent)")
+    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    code = fn(_ptr(partials), splits, partials.stride(0), _ptr(out), _type_code(out.dtype), tokens, inter,
+              float(slope), float(limit or 0.0), float(offset), _stream())  # fmt: skip
     _check(code, "swiglu")
 
 
@@ -238,23 +251,26 @@ def qk_norm_rope_store(
     k_dense: torch.Tensor | None = None,
     v_dense: torch.Tensor | None = None,
     bias: torch.Tensor | None = None,
+    value_dim: int | None = None,
 ) -> None:
     """Per-head RMSNorm of q and k, rotation, and the write of k and v to their cache slots
     (or to dense ``[T, kv_heads * head_dim]`` buffers when ``slot_mapping`` is ``None``).
-    ``qkv`` is ``[S, T, (heads + 2 * kv_heads) * head_dim]`` float32 partial sums; ``bias`` (float32,
-    one value per column of ``qkv``) is added to their sum before anything else."""
+    ``qkv`` is ``[S, T, (heads + kv_heads) * head_dim + kv_heads * value_dim]`` float32 partial sums
+    (``value_dim`` is ``head_dim`` unless given); ``bias`` (float32, one value per column of ``qkv``) is
+    added to their sum before anything else."""
     _need(qkv, torch.float32, "qkv"), _need(q_out, None, "q_out"), _need(positions, torch.int32, "positions")
     splits, tokens, width = qkv.shape
-    if width != (heads + 2 * kv_heads) * head_dim:
-        raise KernelError(f"qkv width {width} is not (heads + 2 kv_heads) * head_dim")
+    value_dim = head_dim if value_dim is None else value_dim
+    if width != (heads + kv_heads) * head_dim + kv_heads * value_dim:
+        raise KernelError(f"qkv width {width} is not (heads + kv_heads) * head_dim + kv_heads * value_dim")
     if kv_heads and slot_mapping is None and (k_dense is None or v_dense is None):
         raise KernelError("either slot_mapping with pages or dense outputs must be given")
     if kv_heads and slot_mapping is not None:
         _need(slot_mapping, torch.int32, "slot_mapping")
         if k_pages is None or v_pages is None or k_pages.dtype != q_out.dtype:
             raise KernelError("pages must be given in the dtype of q_out")
-        if k_pages.shape[1:] != (kv_heads, page_size, head_dim):
-            raise KernelError(f"pages {tuple(k_pages.shape)} do not fit kv_heads/page_size/head_dim")
+        if k_pages.shape[1:] != (kv_heads, page_size, head_dim) or v_pages.shape[1:] != (kv_heads, page_size, value_dim):
+            raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit kv_heads/page_size/head_dim")
     rotary_dim = head_dim
     if cos_sin is not None:
         # a rotation of the first rotary_dim <= head_dim elements of every head; the rest pass through
@@ -269,12 +285,12 @@ def qk_norm_rope_store(
     fn = _fn(
         "elementwise",
         "me_qk_norm_rope_store",
-        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_void_p],
+        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_int, c_void_p],
     )
     code = fn(
         _ptr(qkv), splits, qkv.stride(0), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos_sin), _ptr(positions),
         _ptr(slot_mapping if kv_heads else None), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(k_dense),
-        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, rotary_dim, _ptr(bias), _stream(),
+        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, rotary_dim, _ptr(bias), value_dim, _stream(),
     )  # fmt: skip
     _check(code, "qk_norm_rope_store")
 
@@ -376,6 +392,115 @@ def paged_attention(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,
         scale, window,
     )  # fmt: skip
+
+
+def biased_attention(
+    *, q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads: int, kv_heads: int, head_dim: int,
+    value_dim: int, scale: float, window: int = 0, keep_first: int = 0, r1: torch.Tensor | None = None,
+    r2: torch.Tensor | None = None, talk: torch.Tensor | None = None, spread: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """Attention of the batch's new tokens over their requests' cached keys with value heads of
+    their own width, a window that keeps the first ``keep_first`` tokens, a distance bias ``r1[h] *
+    ln(1 + r2[h] * distance)`` taken off the scores, and the heads' softmax weights mixed by
+    ``talk [heads, heads]`` before they meet the values.  ``out`` is ``[T, heads * value_dim]`` in
+    the dtype of ``q``; with ``talk``, ``spread`` is float32 scratch ``[T, heads, kv_heads,
+    value_dim]``."""
+    _need(q, None, "q"), _need(out, q.dtype, "out"), _need(k_pages, q.dtype, "k_pages"), _need(v_pages, q.dtype, "v_pages")
+    _need(block_table, torch.int32, "block_table"), _need(entry_of_token, torch.int32, "entry_of_token")
+    _need(positions, torch.int32, "positions")
+    tokens = q.shape[0]
+    for name, vector in (("r1", r1), ("r2", r2)):
+        if vector is not None:
+            _need(vector, torch.float32, name)
+            if vector.shape != (heads,):
+                raise KernelError(f"{name} must have one value per head")
+    if (r1 is None) != (r2 is None):
+        raise KernelError("the distance bias takes both of its constants or none")
+    if k_pages.shape[1:] != (kv_heads, k_pages.shape[2], head_dim) or v_pages.shape[1:] != (kv_heads, k_pages.shape[2], value_dim):
+        raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit the head sizes")
+    if talk is not None:
+        _need(talk, torch.float32, "talk"), _need(spread, torch.float32, "spread")
+        if talk.shape != (heads, heads) or spread.numel() < tokens * heads * kv_heads * value_dim:
+            raise KernelError("talk must be [heads, heads] and spread hold [T, heads, kv_heads, value_dim]")
+    fn = _fn(
+        "attention_biased",
+        "me_biased_attention",
+        [c_void_p] * 9 + [c_int, c_float] + [c_int] * 10 + [c_void_p],
+    )
+    code = fn(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _ptr(entry_of_token), _ptr(positions), _ptr(r1), _ptr(r2),
+        _ptr(spread if talk is not None else out), _type_code(q.dtype), float(scale), tokens, heads, kv_heads, head_dim,
+        value_dim, k_pages.shape[2], block_table.shape[1], int(window), int(keep_first), 1 if talk is not None else 0, _stream(),
+    )  # fmt: skip
+    _check(code, "biased_attention")
+    if talk is not None:
+        mix = _fn("attention_biased", "me_mix_heads", [c_void_p] * 3 + [c_int] * 5 + [c_void_p])
+        code = mix(_ptr(spread), _ptr(talk), _ptr(out), _type_code(out.dtype), tokens, heads, kv_heads, value_dim, _stream())
+        _check(code, "mix_heads")
+
+
+def branch_sum(branches: list[tuple[torch.Tensor, float]], out: torch.Tensor) -> None:
+    """``out [T, width] = sum_b factor_b * sum_s partial_b[s]`` for up to four ``[S, T, width]`` float32
+    partial-sum arrays."""
+    _need(out, torch.float32, "out")
+    count = len(branches)
+    if not 1 <= count <= 4:
+        raise KernelError("branch_sum takes one to four branches")
+    for partial, _factor in branches:
+        _need(partial, torch.float32, "partial")
+        if partial.dim() != 3 or tuple(partial.shape[1:]) != tuple(out.shape):
+            raise KernelError(f"branch {tuple(partial.shape)} does not fit out {tuple(out.shape)}")
+    pointers = (c_void_p * count)(*[p.data_ptr() for p, _ in branches])
+    splits = (c_int * count)(*[p.shape[0] for p, _ in branches])
+    strides = (c_longlong * count)(*[p.stride(0) for p, _ in branches])
+    factors = (c_float * count)(*[float(f) for _, f in branches])
+    fn = _fn("elementwise", "me_branch_sum", [c_void_p] * 4 + [c_int, c_void_p, c_int, c_int, c_void_p])
+    code = fn(pointers, splits, strides, factors, count, _ptr(out), out.shape[0], out.shape[1], _stream())
+    _check(code, "branch_sum")
+
+
+def gla_scan(
+    *, proj: torch.Tensor, columns: dict[str, int], a2: torch.Tensor, a2_bias: torch.Tensor, ctx, state: torch.Tensor,
+    out: torch.Tensor, q_scale: float, tau: float, heads: int, dim: int, vdim: int,
+) -> None:  # fmt: skip
+    """The recurrence of gated linear attention over the batch's tokens, entry by entry, from and
+    into each request's state slot.  ``proj`` is ``[S, T, width]`` float32 partial sums whose
+    ``columns`` ``q, k, v, a`` say where each projection starts; ``out`` is float32 ``[T, heads, vdim]``."""
+    _need(proj, torch.float32, "proj"), _need(a2, torch.float32, "a2"), _need(a2_bias, torch.float32, "a2_bias")
+    _need(state, torch.float32, "state"), _need(out, torch.float32, "out")
+    rank = a2.shape[1]
+    if a2.shape != (heads * dim, rank) or a2_bias.shape != (heads * dim,) or state.shape[1:] != (heads, dim, vdim):
+        raise KernelError("gla_scan: decay weights or state do not fit heads/dim/vdim")
+    fn = _fn(
+        "linear_attention",
+        "me_gla_scan",
+        [c_void_p, c_int, c_longlong] + [c_int] * 5 + [c_void_p] * 7 + [c_float, c_float] + [c_int] * 5 + [c_void_p],
+    )
+    code = fn(
+        _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], columns["q"], columns["k"], columns["v"], columns["a"],
+        _ptr(a2), _ptr(a2_bias), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(state), _ptr(out),
+        float(q_scale), float(tau), ctx.num_entries, heads, dim, vdim, rank, _stream(),
+    )  # fmt: skip
+    _check(code, "gla_scan")
+
+
+def gla_finish(
+    *, o: torch.Tensor, proj: torch.Tensor, gate_column: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+    heads: int, vdim: int,
+) -> None:  # fmt: skip
+    """``out = weight * o / rms(o) * silu(gate)`` per (token, head); the gate is a column range of ``proj``."""
+    _need(o, torch.float32, "o"), _need(proj, torch.float32, "proj"), _need(weight, torch.float32, "weight"), _need(out, None, "out")
+    tokens = o.shape[0]
+    fn = _fn(
+        "linear_attention",
+        "me_gla_finish",
+        [c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_float, c_void_p] + [c_int] * 4 + [c_void_p],
+    )
+    code = fn(
+        _ptr(o), _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], gate_column, _ptr(weight), float(eps), _ptr(out),
+        _type_code(out.dtype), tokens, heads, vdim, _stream(),
+    )  # fmt: skip
+    _check(code, "gla_finish")
 
 
 # --------------------------------------------------------------------------------- sampling

@@ -48,7 +48,7 @@ class Replayer:
             dtype=dtype,
             num_blocks=self.num_blocks,
             block_size=block_size,
-            max_num_seqs=MAX_LIVE * 2,
+            max_num_seqs=MAX_LIVE,
             max_num_batched_tokens=max_step_tokens or max(max_tokens, 64),
             max_model_len=self.num_blocks * block_size,
         )
@@ -56,7 +56,7 @@ class Replayer:
             self.runner.layout.groups,
             self.num_blocks,
             block_size,
-            max_num_seqs=MAX_LIVE * 2,
+            max_num_seqs=MAX_LIVE,
             enable_prefix_caching=False,
             slot_groups=self.runner.layout.slot_groups,
         )

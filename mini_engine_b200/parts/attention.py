@@ -11,6 +11,15 @@ query head ``h`` reads KV head ``h // (heads / kv_heads)``, scores are scaled by
 The three projections run as one product on the row-concatenated weight, which leaves every
 output element's sum unchanged.  Per-head norm, rotation and the cache write are one kernel.
 All sizes and constants are constructor arguments; the part does not know its model.
+
+Options beyond that model, each switched on by the spec: no position encoding at all
+(``position_encoding=None``); value heads of their own width (``value_dim``); a window that keeps
+the first ``keep_first`` tokens of the sequence readable for good (query ``p`` sees key ``j <= p``
+when ``p - j < window`` or ``j < keep_first``); a distance bias taken off the scores,
+``r1[h] * ln(1 + r2[h] * (p - j))`` with two learned numbers per head (``distance_bias``); and the
+heads' softmax weights mixed by a learned ``[heads, heads]`` matrix before they meet the values
+(``talking_heads``: ``w'_h = sum_g T[h, g] w_g``, head ``h`` reads its own KV head with ``w'_h``).  The
+last four run in the kernels of ``csrc/attention_biased.cu``.
 """
 
 from __future__ import annotations
@@ -45,17 +54,32 @@ class GroupedQueryAttention(Mixer):
         num_heads: int,
         kv_heads: int,
         head_dim: int,
-        position_encoding: PartSpec,
+        position_encoding: PartSpec | None,
         qk_norm_eps: float | None = None,
         window: int | None = None,
         scale: float | None = None,
         reads_shared_cache: bool = False,
         qkv_bias: bool = False,
         names: Mapping[str, str] | None = None,
+        value_dim: int | None = None,
+        keep_first: int = 0,
+        distance_bias: bool = False,
+        talking_heads: bool = False,
     ):
         if num_heads % kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of kv_heads ({kv_heads})")
-        ops.check_attention_sizes(head_dim, num_heads, kv_heads)
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        self.keep_first = int(keep_first) if window else 0
+        self.distance_bias, self.talking_heads = bool(distance_bias), bool(talking_heads)
+        # Whether the step runs in the kernels that know these options (any head size) or in the plain ones.
+        self.extended = bool(self.value_dim != head_dim or self.keep_first or distance_bias or talking_heads)
+        if self.extended:
+            if reads_shared_cache or qkv_bias:
+                raise ValueError("the extended attention options do not combine with a shared cache or biases")
+            if head_dim < 1 or self.value_dim < 1 or keep_first < 0:
+                raise ValueError("head sizes must be positive and keep_first must not be negative")
+        else:
+            ops.check_attention_sizes(head_dim, num_heads, kv_heads)
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden_size, num_heads, kv_heads, head_dim
         self.qk_norm_eps = qk_norm_eps
         self.window = window
@@ -72,9 +96,15 @@ class GroupedQueryAttention(Mixer):
             "q_bias": "q_proj.bias",
             "k_bias": "k_proj.bias",
             "v_bias": "v_proj.bias",
+            "r1": "distance_bias.r1",
+            "r2": "distance_bias.r2",
+            "talk": "talking_heads.weight",
         }
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
-        self.position = build_part("position_encoding", position_encoding, prefix, hidden_size)
+        self.position = None
+        if position_encoding is not None:
+            self.position = build_part("position_encoding", position_encoding, prefix, hidden_size)
+        self.r1 = self.r2 = self.talk = None
         self.qkv: Linear | None = None
         self.out: Linear | None = None
         self.q_norm: torch.Tensor | None = None
@@ -84,7 +114,8 @@ class GroupedQueryAttention(Mixer):
     # ------------------------------------------------------------------ declarations
 
     def paged_cache(self) -> PagedCacheSpec:
-        return PagedCacheSpec(self.kv_heads, self.head_dim, self.window)
+        value_dim = None if self.value_dim == self.head_dim else self.value_dim
+        return PagedCacheSpec(self.kv_heads, self.head_dim, self.window, value_dim, self.keep_first)
 
     def weight_specs(self) -> list[WeightSpec]:
         d, n = self.head_dim, self.names
@@ -92,9 +123,13 @@ class GroupedQueryAttention(Mixer):
         if not self.reads_shared_cache:
             specs += [
                 WeightSpec(n["k"], (self.kv_heads * d, self.hidden)),
-                WeightSpec(n["v"], (self.kv_heads * d, self.hidden)),
+                WeightSpec(n["v"], (self.kv_heads * self.value_dim, self.hidden)),
             ]
-        specs.append(WeightSpec(n["o"], (self.hidden, self.heads * d)))
+        specs.append(WeightSpec(n["o"], (self.hidden, self.heads * self.value_dim)))
+        if self.distance_bias:
+            specs += [WeightSpec(n[key], (self.heads,), role="vector", init="positive") for key in ("r1", "r2")]
+        if self.talking_heads:
+            specs.append(WeightSpec(n["talk"], (self.heads, self.heads), role="vector", init="ones_normal"))
         if self.qk_norm_eps is not None:
             specs.append(WeightSpec(n["q_norm"], (d,), role="vector", init="ones_normal"))
             if not self.reads_shared_cache:
@@ -104,7 +139,7 @@ class GroupedQueryAttention(Mixer):
             if not self.reads_shared_cache:
                 specs.append(WeightSpec(n["k_bias"], (self.kv_heads * d,), role="vector"))
                 specs.append(WeightSpec(n["v_bias"], (self.kv_heads * d,), role="vector"))
-        return specs + self.position.weight_specs()
+        return specs + (self.position.weight_specs() if self.position is not None else [])
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
@@ -121,7 +156,12 @@ class GroupedQueryAttention(Mixer):
             if not self.reads_shared_cache:
                 parts += [tensors[n["k_bias"]], tensors[n["v_bias"]]]
             self.bias = torch.cat(parts).contiguous()
-        self.position.load(tensors)
+        if self.distance_bias:
+            self.r1, self.r2 = tensors[n["r1"]], tensors[n["r2"]]
+        if self.talking_heads:
+            self.talk = tensors[n["talk"]]
+        if self.position is not None:
+            self.position.load(tensors)
 
     # ------------------------------------------------------------------------ step
 
@@ -130,21 +170,21 @@ class GroupedQueryAttention(Mixer):
         kv_in = 0 if self.reads_shared_cache else self.kv_heads
         qkv = self.qkv.forward(h, ctx, "attn.qkv")
         q = ctx.buffer("attn.q", (tokens, self.heads * d), ctx.dtype)
-        table = self.position.step_angles(ctx)
+        table = self.position.step_angles(ctx) if self.position is not None else None
         slots = ctx.slot_mapping[cache.group]
         args: dict[str, Any] = dict(
             qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, q_weight=self.q_norm,
             k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, positions=ctx.positions, q_out=q,
-            page_size=ctx.page_size, bias=self.bias,
+            page_size=ctx.page_size, bias=self.bias, value_dim=self.value_dim,
         )  # fmt: skip
         if kv_in and not cache.writes:
             # This execution reads another entry's cache: its own keys and values are not kept.
             unused_k = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
             unused_v = ctx.buffer("attn.v_new", (tokens, kv_in * d), ctx.dtype)
             ops.qk_norm_rope_store(**args, cos_sin=table, k_dense=unused_k, v_dense=unused_v)
-            if table is None:
+            if table is None and self.position is not None:
                 self.position.apply(q.view(tokens, self.heads, d), unused_k.view(tokens, kv_in, d), ctx.positions)
-        elif table is not None or kv_in == 0:
+        elif table is not None or kv_in == 0 or self.position is None:
             ops.qk_norm_rope_store(
                 **args, cos_sin=table, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v
             )
@@ -154,6 +194,19 @@ class GroupedQueryAttention(Mixer):
             ops.qk_norm_rope_store(**args, cos_sin=None, k_dense=k_new, v_dense=v_new)
             self.position.apply(q.view(tokens, self.heads, d), k_new.view(tokens, kv_in, d), ctx.positions)
             ops.kv_store(k_new, v_new, slots, cache.k, cache.v, kv_in, d, ctx.page_size)
+        if self.extended:
+            out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
+            spread = None
+            if self.talk is not None:
+                spread = ctx.buffer("attn.spread", (tokens, self.heads * self.kv_heads * self.value_dim), torch.float32)
+            ops.biased_attention(
+                q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group],
+                entry_of_token=ctx.entry_of_token, positions=ctx.positions, out=out, heads=self.heads,
+                kv_heads=self.kv_heads, head_dim=d, value_dim=self.value_dim, scale=self.scale,
+                window=self.window or 0, keep_first=self.keep_first, r1=self.r1, r2=self.r2, talk=self.talk,
+                spread=spread,
+            )  # fmt: skip
+            return self.out.forward(out, ctx, "attn.o")
         out = ctx.buffer("attn.out", (tokens, self.heads * d), ctx.dtype)
         ops.paged_attention(
             q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx,

@@ -37,13 +37,21 @@ class PagedCacheSpec:
 
     ``window`` is ``None`` when every key is kept; else only the last ``window`` positions
     are ever read and pages wholly behind the window are given back while the request runs.
-    Mixers with an equal spec share one cache group (one page pool, one block table per
-    request).
+    With a window, ``keep_first`` tokens at the start of the sequence stay readable for good (their
+    pages are never given back).  ``value_dim`` is the width of a value head when it differs from
+    ``head_dim``.  Mixers with an equal spec share one cache group (one page pool, one block table
+    per request).
     """
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    keep_first: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -62,18 +70,24 @@ class Residual:
     """The residual stream ``x [T, hidden]`` (float32) and a pending addend.
 
     ``pending`` is ``None`` or a float32 tensor ``[S, T, hidden]`` whose ``S`` slices (the
-    partial sums of a split matrix product) are all still to be added to ``x``.
+    partial sums of a split matrix product) are all still to be added to ``x``; with
+    ``pending_scale`` (float32 ``[hidden]``, a layer scale) their sum is multiplied column by column
+    before it is added.
     """
 
     x: torch.Tensor
     pending: torch.Tensor | None = None
+    pending_scale: torch.Tensor | None = None
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta: torch.Tensor, scale: torch.Tensor | None = None) -> None:
         if self.pending is not None:
             raise RuntimeError("a pending output must be consumed by a norm before the next is set")
         if delta.dim() == 2:
             delta = delta.unsqueeze(0)
-        self.pending = delta
+        self.pending, self.pending_scale = delta, scale
+
+    def clear(self) -> None:
+        self.pending = self.pending_scale = None
 
 
 @dataclass
@@ -236,7 +250,8 @@ class Block(Part):
         return self.norms["feed_forward"]
 
     def parts(self) -> list[Part]:
-        return [self.mixer, self.feed_forward, *(self.norms[name] for name in self.NORMS)]
+        whole = [self.mixer, self.feed_forward, *(self.norms[name] for name in self.NORMS)]
+        return [part for part in whole if part is not None]  # a layer may have no feed-forward
 
     def weight_specs(self) -> list[WeightSpec]:
         return [spec for part in self.parts() for spec in part.weight_specs()]

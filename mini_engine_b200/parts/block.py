@@ -2,7 +2,10 @@
 
 from __future__ import annotations
 
+import torch
+
 from mini_engine_b200.parts.base import Block, LayerCache, Residual, StepContext, register
+from mini_engine_b200.weights.loader import WeightSpec
 
 
 @register("block", "prenorm")
@@ -19,3 +22,59 @@ class PreNormBlock(Block):
         state.add(self.mixer.forward(h, ctx, cache))
         h = self.feed_forward_norm.forward(state, ctx, ctx.dtype)
         state.add(self.feed_forward.forward(h, ctx))
+
+
+class _LayerScales:
+    """Per-channel multipliers of a part's output ("layer scale"), one vector per part."""
+
+    def __init__(self, prefix: str, hidden_size: int, names):
+        self.hidden = hidden_size
+        self.scale_names = {key: prefix + name for key, name in names.items()}
+        self.scales: dict[str, torch.Tensor] = {}
+
+    def specs(self) -> list[WeightSpec]:
+        return [WeightSpec(name, (self.hidden,), role="vector", init="ones_normal") for name in self.scale_names.values()]
+
+    def load(self, tensors) -> None:
+        self.scales = {key: tensors[name] for key, name in self.scale_names.items()}
+
+
+@register("block", "prenorm_scaled")
+class ScaledPreNormBlock(Block):
+    """``h = x + s_m * mixer(norm(x))``, ``y = h + s_f * feed_forward(norm(h))`` with the per-channel
+    vectors ``s_m``, ``s_f`` of the layer (a layer scale).  The products and the sums happen inside
+    the norm that follows, in 32-bit: ``x + s * (sum of the part's partial sums)``."""
+
+    capturable = True
+
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str, hidden_size: int, scale_names, unused_names=()):
+        """``unused_names``: tensors of the layer that a checkpoint may carry although the layer has
+        no use for them (the feed-forward's norm and scale of a layer without a feed-forward)."""
+        super().__init__(mixer, feed_forward, norms)
+        self.unused = [prefix + name for name in unused_names]
+        wanted = {"mixer"} if feed_forward is None else {"mixer", "feed_forward"}
+        if set(scale_names) != wanted:
+            raise ValueError(f"the layer scales must be named for {sorted(wanted)}, got {sorted(scale_names)}")
+        self.layer_scales = _LayerScales(prefix, hidden_size, scale_names)
+
+    def weight_specs(self) -> list[WeightSpec]:
+        unused = [WeightSpec(name, (), role="vector", optional=True) for name in self.unused]
+        return super().weight_specs() + self.layer_scales.specs() + unused
+
+    def load(self, tensors) -> None:
+        super().load(tensors)
+        self.layer_scales.load(tensors)
+
+    def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
+        h = self.mixer_norm.forward(state, ctx, ctx.dtype)
+        state.add(self.mixer.forward(h, ctx, cache), self.layer_scales.scales["mixer"])
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.forward(state, ctx, ctx.dtype)
+            state.add(self.feed_forward.forward(h, ctx), self.layer_scales.scales["feed_forward"])
+
+
+@register("block", "prenorm_scaled_mixer_only")
+class ScaledMixerOnlyBlock(ScaledPreNormBlock):
+    """The same arrangement for a layer without a feed-forward: one norm, one layer scale."""
+
+    NORMS = ("mixer",)

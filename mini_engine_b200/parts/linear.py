@@ -74,9 +74,13 @@ class Linear:
 
 
 class GatedLinear:
-    """``silu(x Wg^T) * (x Wu^T)`` from the row-concatenated weight ``[2 * inter, in]``."""
+    """``silu(x Wg^T) * (x Wu^T)`` from the row-concatenated weight ``[2 * inter, in]``; with a
+    ``slope``, a ``limit`` or an ``offset`` the gated unit of :func:`ops.swiglu` with those constants
+    (as a kernel of its own behind the product: the fused epilogue is SwiGLU proper)."""
 
-    def __init__(self, gate_up: torch.Tensor):
+    def __init__(self, gate_up: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0):
+        self.slope, self.limit, self.offset = slope, limit, offset
+        self.plain = slope == 1.0 and limit is None and offset == 0.0
         self.weight = gate_up
         self.inter = gate_up.shape[0] // 2
         self.in_features = gate_up.shape[1]
@@ -91,9 +95,9 @@ class GatedLinear:
         tokens = x.shape[0]
         act = ctx.buffer(name + ".act", (tokens, self.inter), x.dtype)
         fused = tokens >= GATED_FUSED_MIN_TOKENS and (tokens > DECODE_TOKENS or self.inter >= GATED_STACKED_MIN_FEATURES)
-        if self.tensor_core and fused:
+        if self.tensor_core and fused and self.plain:
             ops.gemm_tensor_core_swiglu(self.plan, x, act)
             return act
         both = self.linear.forward(x, ctx, name + ".gate_up")
-        ops.swiglu(both, act)
+        ops.swiglu(both, act, self.slope, self.limit, self.offset)
         return act

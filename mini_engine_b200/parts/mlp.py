@@ -4,6 +4,10 @@
 (src/mini_engine/model.py:122-131 of YuvGev00/mini-engine).  Gate and up run as one product
 on the row-concatenated weight; on the tensor-core path the activation is applied in that
 product's epilogue, so the ``[T, 2 * inter]`` intermediate never reaches memory.
+
+The gate has three constants for models whose gated unit differs: ``y = g * sigmoid(gate_slope * g) *
+(u + up_offset)`` with ``g = min(x Wg^T, limit)`` and ``u = clamp(x Wu^T, -limit, limit)`` when a
+``limit`` is given.  Slope 1, no limit and offset 0 are SwiGLU.
 """
 
 from __future__ import annotations
@@ -29,10 +33,16 @@ class GatedMLP(FeedForward):
         intermediate_size: int,
         activation: str = "silu",
         names: Mapping[str, str] | None = None,
+        gate_slope: float = 1.0,
+        limit: float | None = None,
+        up_offset: float = 0.0,
     ):
         if activation != "silu":
             raise ValueError(f"gated_mlp implements the 'silu' gate only, got {activation!r}")
+        if limit is not None and not limit > 0:
+            raise ValueError(f"the limit of the gated unit must be positive, got {limit}")
         self.hidden, self.inter = hidden_size, intermediate_size
+        self.gate_slope, self.limit, self.up_offset = float(gate_slope), limit, float(up_offset)
         defaults = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
         self.gate_up: GatedLinear | None = None
@@ -48,7 +58,10 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
-        self.gate_up = GatedLinear(torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous())
+        self.gate_up = GatedLinear(
+            torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous(),
+            slope=self.gate_slope, limit=self.limit, offset=self.up_offset,
+        )  # fmt: skip
         self.down = Linear(tensors[n["down"]])
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:

@@ -28,7 +28,7 @@ from mini_engine_b200.parts.base import (
 from mini_engine_b200.weights.loader import WeightSpec
 
 # Importing the built-in parts registers them.
-from mini_engine_b200.parts import attention, block, ends, mlp, norms, rotary  # noqa: F401,E402
+from mini_engine_b200.parts import attention, block, ends, linear_attention, mlp, norms, parallel, rotary  # noqa: F401,E402
 
 
 def build_block(spec: ModelSpec, index: int) -> Block:
@@ -39,11 +39,13 @@ def build_block(spec: ModelSpec, index: int) -> Block:
         raise KeyError(f"no block named {layer.block!r}; registered: {', '.join(sorted(BLOCKS))}")
     hidden = spec.hidden_size
     norms = {name: build_part("norm", part, layer.prefix, hidden) for name, part in layer.named_norms().items()}
-    return BLOCKS[layer.block](
-        build_part("mixer", layer.mixer, layer.prefix, hidden),
-        build_part("feed_forward", layer.feed_forward, layer.prefix, hidden),
-        norms,
-    )
+    feed_forward = None
+    if layer.feed_forward is not None:
+        feed_forward = build_part("feed_forward", layer.feed_forward, layer.prefix, hidden)
+    mixer = build_part("mixer", layer.mixer, layer.prefix, hidden)
+    if layer.block_params:  # an arrangement with weights or constants of its own
+        return BLOCKS[layer.block](mixer, feed_forward, norms, prefix=layer.prefix, hidden_size=hidden, **dict(layer.block_params))
+    return BLOCKS[layer.block](mixer, feed_forward, norms)
 
 
 class DecoderModel:
@@ -109,10 +111,10 @@ class DecoderModel:
         count = logits_rows.shape[0]
         if count == 0:
             # Nothing is wanted, but the last pending sum must not be left on the state.
-            state.pending = None
+            state.clear()
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         rows = self.final_norm.forward(state, ctx, ctx.dtype, rows=logits_rows)
-        state.pending = None
+        state.clear()
         return self.head.forward(rows, ctx)
 
 

@@ -22,22 +22,30 @@ from mini_engine_b200.weights.loader import WeightSpec
 class RMSNorm(Norm):
     capturable = True
 
-    def __init__(self, prefix: str, hidden_size: int, *, name: str, eps: float, dim: int | None = None):
+    def __init__(
+        self, prefix: str, hidden_size: int, *, name: str, eps: float, dim: int | None = None, offset: float = 0.0
+    ):
+        """``offset``: what is added to the stored weight before it multiplies (1 for a checkpoint that
+        keeps its norm weights around zero: ``y = (1 + w) * x / rms(x)``); the sum is formed once, in 32-bit."""
         self.weight_name = prefix + name
         self.dim = dim or hidden_size
         self.eps = float(eps)
+        self.offset = float(offset)
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(self.weight_name, (self.dim,), role="vector", init="ones_normal")]
+        init = "ones_normal" if self.offset == 0.0 else "small_normal"
+        return [WeightSpec(self.weight_name, (self.dim,), role="vector", init=init)]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name]
+        if self.offset != 0.0:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def forward(self, state: Residual, ctx: StepContext, out_dtype, rows=None) -> torch.Tensor:
         count = state.x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm.out" if rows is None else "norm.rows", (count, self.dim), out_dtype)
-        ops.add_rmsnorm(state.x, state.pending, self.weight, self.eps, out, rows)
+        ops.add_rmsnorm(state.x, state.pending, self.weight, self.eps, out, rows, state.pending_scale)
         if rows is None:
-            state.pending = None
+            state.clear()
         return out

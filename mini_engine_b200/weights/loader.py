@@ -53,8 +53,11 @@ class WeightSpec:
     name: str  # full checkpoint name
     shape: tuple[int, ...]
     role: str = "matrix"  # "matrix", "vector" or "table"
-    init: str = "normal"  # random-weights mode: "normal" (N(0, 0.02)) or "ones_normal" (1 + N(0, 0.1))
+    # random-weights mode: "normal" (N(0, 0.02)), "ones_normal" (1 + N(0, 0.1)), "small_normal" (N(0, 0.1),
+    # weights kept around zero) or "positive" (0.05 + |N(0, 0.1)|)
+    init: str = "normal"
     alias_of: str | None = None  # tied tensor: use that tensor's storage; a stored copy is ignored
+    optional: bool = False  # a tensor that a checkpoint may carry although this model has no use for it: never loaded
 
 
 def _target_dtype(role: str, compute: torch.dtype) -> torch.dtype:
@@ -76,6 +79,8 @@ def check_specs(specs: Iterable[WeightSpec], entries: dict[str, tuple[torch.dtyp
         if spec.alias_of is not None:
             if spec.alias_of not in wanted:
                 other.append(f"{spec.name} is tied to {spec.alias_of}, which the model does not declare")
+            continue
+        if spec.optional:
             continue
         if spec.name not in entries:
             missing.append(spec.name)
@@ -103,7 +108,7 @@ def load_weights(
     check_specs(specs, entries)
     out: dict[str, torch.Tensor] = {}
     for spec in specs:
-        if spec.alias_of is None:
+        if spec.alias_of is None and not spec.optional:
             host = where[spec.name].tensor(spec.name)
             out[spec.name] = host.to(device=device, dtype=_target_dtype(spec.role, compute)).contiguous()
     for spec in specs:
@@ -121,7 +126,7 @@ def place_tensors(
     out = {
         s.name: tensors[s.name].to(device=device, dtype=_target_dtype(s.role, compute)).contiguous()
         for s in specs
-        if s.alias_of is None
+        if s.alias_of is None and not s.optional
     }
     for s in specs:
         if s.alias_of is not None:

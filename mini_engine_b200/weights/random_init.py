@@ -82,6 +82,11 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu",
     if spec.init == "ones_normal":
         values = values * NORM_STD  # two roundings, the same two everywhere (no fused multiply-add)
         values = values + 1.0
+    elif spec.init == "small_normal":
+        values = values * NORM_STD
+    elif spec.init == "positive":
+        values = values.abs() * NORM_STD
+        values = values + 0.05
     else:
         values = values * (MATRIX_STD * scale)
     return values.to(dtype)
@@ -93,7 +98,7 @@ def random_tensors(
     """``scale`` widens the matrices' standard deviation (tests use it to make logits
     peaked, so that an argmax cannot flip on rounding alone)."""
     return {
-        s.name: random_tensor(s, seed, dtype, device, scale) for s in specs if s.alias_of is None
+        s.name: random_tensor(s, seed, dtype, device, scale) for s in specs if s.alias_of is None and not s.optional
     }
 
 
