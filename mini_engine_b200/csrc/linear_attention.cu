@@ -51,7 +51,8 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
     float* q_s = staged;                          // [SCAN_CHUNK][DIMP]
     float* k_s = q_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][DIMP]
     float* d_s = k_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][DIMP] decay
-    float* r_s = d_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][rank] low-rank sums
+    float* v_s = d_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][32] this warp's value columns
+    float* r_s = v_s + SCAN_CHUNK * 32;           // [SCAN_CHUNK][rank] low-rank sums
     const int entry = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int column = blockIdx.z * 32 + lane;
     const bool live = column < a.vdim;
@@ -95,19 +96,18 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
             }
             q_s[i] = q, k_s[i] = k, d_s[i] = decay;
         }
-        __syncwarp();
-        float v[SCAN_CHUNK];
-#pragma unroll
-        for (int t = 0; t < SCAN_CHUNK; ++t) {
-            v[t] = 0.0f;
-            if (live && t < count) {
+        for (int t = 0; t < count; ++t) {
+            float value = 0.0f;
+            if (live) {
                 const float* src = a.proj + static_cast<size_t>(chunk + t) * a.width + a.v_col + head * a.vdim + column;
-                for (int p = 0; p < a.splits; ++p) v[t] += src[p * a.split_stride];
+                for (int p = 0; p < a.splits; ++p) value += src[p * a.split_stride];
             }
+            v_s[t * 32 + lane] = value;
         }
-#pragma unroll
-        for (int t = 0; t < SCAN_CHUNK; ++t) {
-            if (t >= count) break;
+        __syncwarp();
+#pragma unroll 1
+        for (int t = 0; t < count; ++t) {
+            const float v = v_s[t * 32 + lane];
             const float4* q4 = reinterpret_cast<const float4*>(q_s + t * DIMP);
             const float4* k4 = reinterpret_cast<const float4*>(k_s + t * DIMP);
             const float4* d4 = reinterpret_cast<const float4*>(d_s + t * DIMP);
@@ -115,10 +115,10 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
 #pragma unroll
             for (int d = 0; d < DIMP; d += 4) {
                 const float4 qq = q4[d / 4], kk = k4[d / 4], dd = d4[d / 4];
-                s[d + 0] = fmaf(dd.x, s[d + 0], kk.x * v[t]);
-                s[d + 1] = fmaf(dd.y, s[d + 1], kk.y * v[t]);
-                s[d + 2] = fmaf(dd.z, s[d + 2], kk.z * v[t]);
-                s[d + 3] = fmaf(dd.w, s[d + 3], kk.w * v[t]);
+                s[d + 0] = fmaf(dd.x, s[d + 0], kk.x * v);
+                s[d + 1] = fmaf(dd.y, s[d + 1], kk.y * v);
+                s[d + 2] = fmaf(dd.z, s[d + 2], kk.z * v);
+                s[d + 3] = fmaf(dd.w, s[d + 3], kk.w * v);
                 o = fmaf(s[d + 0], qq.x, o);
                 o = fmaf(s[d + 1], qq.y, o);
                 o = fmaf(s[d + 2], qq.z, o);
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
 template <int DIMP>
 static int launch_scan(const ScanArgs& a, int entries, cudaStream_t stream) {
     static SharedMemoryOptIn opt_in;
-    const size_t smem = (static_cast<size_t>(3) * SCAN_CHUNK * DIMP + static_cast<size_t>(SCAN_CHUNK) * a.rank) * sizeof(float);
+    const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (3 * DIMP + 32 + a.rank)) * sizeof(float);
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
     if (smem > 48 * 1024) {
         const int code = opt_in(gla_scan_kernel<DIMP>, static_cast<int>(smem));

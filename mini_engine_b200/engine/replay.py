@@ -22,7 +22,7 @@ from pathlib import Path
 import torch
 
 PAGE_SIZE = 16  # tokens per page; --max-tokens counts requests rounded up to 64, a multiple of it
-MAX_LIVE = 4
+MAX_LIVE = 4  # requests that are live at the same time: that many state slots, used again as requests end
 
 
 class Replayer:
@@ -35,6 +35,7 @@ class Replayer:
         max_tokens: int,
         block_size: int = PAGE_SIZE,
         max_step_tokens: int | None = None,
+        max_live: int = MAX_LIVE,
     ):
         from mini_engine_b200.cache.manager import CacheManager
         from mini_engine_b200.engine.loading import load_model
@@ -48,7 +49,7 @@ class Replayer:
             dtype=dtype,
             num_blocks=self.num_blocks,
             block_size=block_size,
-            max_num_seqs=MAX_LIVE,
+            max_num_seqs=max_live,
             max_num_batched_tokens=max_step_tokens or max(max_tokens, 64),
             max_model_len=self.num_blocks * block_size,
         )
@@ -56,7 +57,7 @@ class Replayer:
             self.runner.layout.groups,
             self.num_blocks,
             block_size,
-            max_num_seqs=MAX_LIVE,
+            max_num_seqs=max_live,
             enable_prefix_caching=False,
             slot_groups=self.runner.layout.slot_groups,
         )
@@ -78,7 +79,8 @@ class Replayer:
             if not self.manager.try_allocate(cache, held + len(tokens)):
                 raise MemoryError(
                     f"step {record.get('step')}: request {name!r} needs {held + len(tokens)} tokens but the "
-                    f"pool of {self.num_blocks * self.block_size} tokens (--max-tokens) is exhausted"
+                    f"pool of {self.num_blocks * self.block_size} tokens (--max-tokens) or the "
+                    f"{self.manager.slots.num_slots} state slots (--max-live) are exhausted"
                 )
             entries.append(StepEntry(cache, held, tokens, tuple(item.get("want", ()))))
             self.live[name][1] = held + len(tokens)
@@ -106,12 +108,13 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     parser.add_argument("--block-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     parser.add_argument("--max-step-tokens", type=int, default=None, help="most tokens in one step")
+    parser.add_argument("--max-live", type=int, default=MAX_LIVE, help="most requests that are live at the same time")
     args = parser.parse_args(argv)
 
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
-    replayer = Replayer(args.model, dtype, args.max_tokens, args.block_size, args.max_step_tokens)
+    replayer = Replayer(args.model, dtype, args.max_tokens, args.block_size, args.max_step_tokens, args.max_live)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -56,11 +56,11 @@ def expected_logits(folder, dtype_name, requests):
     return expected
 
 
-def run_in_process(folder, dtype_name, steps, block_size, max_tokens=None, max_step_tokens=512):
+def run_in_process(folder, dtype_name, steps, block_size, max_tokens=None, max_step_tokens=512, max_live=4):
     from mini_engine_b200.engine.replay import Replayer
 
     max_tokens = max_tokens or schedules.peak_live_tokens(steps)
-    replayer = Replayer(folder, DTYPES[dtype_name], max_tokens, block_size, max_step_tokens=max_step_tokens)
+    replayer = Replayer(folder, DTYPES[dtype_name], max_tokens, block_size, max_step_tokens=max_step_tokens, max_live=max_live)
     outputs = {}
     for record in steps:
         logits = replayer.step(record)
@@ -156,7 +156,7 @@ def test_one_mixed_step_of_real_sizes(dtype_name, layer_of_8b_folder):
     last_entries += [{"id": name, "tokens": [toks[-1]], "want": [0]} for name, toks in decoding.items()]
     steps.append({"step": number, "entries": last_entries, "end": ["p0", *decoding]})
     peak = schedules.peak_live_tokens(steps)
-    got = run_in_process(folder, dtype_name, steps, PAGE_SIZE["8B"], max_tokens=peak, max_step_tokens=640)
+    got = run_in_process(folder, dtype_name, steps, PAGE_SIZE["8B"], max_tokens=peak, max_step_tokens=640, max_live=6)
     compare(got, expected_logits(folder, dtype_name, requests), requests, TOLERANCE[dtype_name], kind=f"{dtype_name} at 8B sizes")
 
 
