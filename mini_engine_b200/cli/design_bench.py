@@ -1,0 +1,267 @@
+"""Prefill and decode throughput of the Pimezen design beside Qwen3 dense at equal layer sizes.
+
+    python -m mini_engine_b200.cli.design_bench [--sizes 1b,8b] [--steps K] [--warmup W]      (or: bench.py --design pimezen)
+
+For each size both models get the same width, feed-forward width, head counts, head size, layer count
+and vocabulary, seeded random bfloat16 weights, and the same two workloads: one prompt of 2,048 tokens
+(device time of the step, tokens per second) and decode steps of 8 requests at 2,048-token contexts as
+captured graphs.  Pimezen's softmax attention has a window of 1,024 tokens that keeps the first 64; its
+linear attention has as many heads.  Beside the step times, every kernel class is timed inside one eager
+prompt step and one eager decode step (CUDA events around each launch) and set against its roofline: the
+longer of (algorithmic bytes / measured copy bandwidth) and (algorithmic flops / measured bfloat16 peak)
+over the time it took.  One JSON line is printed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+PROMPT, CONTEXT, BATCH, BLOCK = 2048, 2048, 8, 16
+WINDOW, KEEP_FIRST = 1024, 64
+
+SIZES = {
+    # width, ff, heads, kv_heads, head size, layers, vocabulary; linear attention: key and value width per head, decay rank
+    "1b": dict(width=2048, ff=6144, heads=16, kv_heads=8, head_dim=128, layers=4, vocab=32768, lin_dim=64, lin_vdim=128, rank=64),
+    "8b": dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=4, vocab=32768, lin_dim=128, lin_vdim=128, rank=64),
+}
+TIMED = ("biased_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
+         "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding")  # fmt: skip
+
+
+def configs(size: dict):
+    from mini_engine_b200.config import PimezenConfig, Qwen3Config
+
+    qwen = Qwen3Config(
+        vocab_size=size["vocab"], hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=size["layers"],
+        num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"], rms_norm_eps=1e-6,
+        rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=True,
+    )  # fmt: skip
+    layer = {
+        "type": "parallel",
+        "mixer": {
+            "left": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["head_dim"], "vdim": size["head_dim"],
+                     "scale": size["head_dim"] ** -0.5, "mask": {"size": WINDOW, "keep_first": KEEP_FIRST}},
+            "right": {"heads": size["heads"], "dim": size["lin_dim"], "vdim": size["lin_vdim"], "tau": 16.0, "decay_rank": size["rank"]},
+            "left_scale": 1.0, "right_scale": 1.0,
+        },
+        "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0},
+    }  # fmt: skip
+    pimezen = PimezenConfig.from_dict({"architecture": "Pimezen", "vocab": size["vocab"], "width": size["width"],
+                                       "norm": {"eps": 1e-6}, "layers": [layer] * size["layers"]})  # fmt: skip
+    return {"pimezen": pimezen, "qwen3": qwen}
+
+
+class KernelTimes:
+    """While open, every launch through the named bindings is bracketed by two CUDA events."""
+
+    def __init__(self):
+        self.events: list[tuple[str, object, object]] = []
+
+    def __enter__(self):
+        import torch
+
+        from mini_engine_b200.csrc import ops
+
+        self.saved = {name: getattr(ops, name) for name in TIMED}
+        for name, function in self.saved.items():
+            def timed(*args, _name=name, _function=function, **kwargs):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                result = _function(*args, **kwargs)
+                end.record()
+                self.events.append((_name, start, end))
+                return result
+
+            setattr(ops, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        from mini_engine_b200.csrc import ops
+
+        for name, function in self.saved.items():
+            setattr(ops, name, function)
+
+    def totals(self) -> dict[str, float]:
+        import torch
+
+        torch.cuda.synchronize()
+        out: dict[str, float] = {}
+        for name, start, end in self.events:
+            out[name] = out.get(name, 0.0) + start.elapsed_time(end) * 1e3  # microseconds
+        return out
+
+
+def visible_sum(tokens_from: int, tokens_to: int, window: int | None, keep_first: int) -> int:
+    """Sum over query positions [from, to) of the keys each sees."""
+    total = 0
+    for p in range(tokens_from, tokens_to):
+        if window is None or p < window:
+            total += p + 1
+        else:
+            total += window + min(keep_first, p - window + 1)
+    return total
+
+
+def rooflines(design: str, size: dict, peaks: dict) -> dict:
+    """Algorithmic bytes and flops of one layer's attention-class kernels, for the prompt and for the decode step."""
+    h, g, d = size["heads"], size["kv_heads"], size["head_dim"]
+    bw, flops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {}
+
+    def bound(name, nbytes, nflops):
+        out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
+
+    window = WINDOW if design == "pimezen" else None
+    keep = KEEP_FIRST if design == "pimezen" else 0
+    seen_prompt = visible_sum(0, PROMPT, window, keep)
+    seen_decode = BATCH * visible_sum(CONTEXT, CONTEXT + 1, window, keep)
+    mixing = 2 * h * h if design == "pimezen" else 0  # flops per (query, key) of mixing the heads' weights
+    kind = "biased_attention" if design == "pimezen" else "paged_attention"
+    bound(f"prompt.{kind}", PROMPT * (2 * h * d + 2 * g * d) * 2, seen_prompt * (4 * h * d + mixing))
+    bound(f"decode.{kind}", seen_decode * g * 2 * d * 2 + BATCH * 2 * h * d * 2, seen_decode * (4 * h * d + mixing))
+    if design == "pimezen":
+        ld, lv, rank = size["lin_dim"], size["lin_vdim"], size["rank"]
+        state = h * ld * lv * 4
+        row = (2 * h * ld + h * lv + rank) * 4
+        bound("prompt.gla_scan", PROMPT * (row + h * lv * 4) + 2 * state, PROMPT * h * ld * lv * 4)
+        bound("decode.gla_scan", BATCH * (8 * row + h * lv * 4 + 2 * state), BATCH * h * ld * lv * 4)
+    return out
+
+
+def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dict) -> dict:
+    import torch
+
+    from mini_engine_b200 import EngineConfig, LLMEngine
+    from mini_engine_b200.csrc import ops
+    from mini_engine_b200.engine.runner import StepEntry
+
+    total_steps = steps + warmup + 8
+    pages = -(-(CONTEXT + total_steps + 1) // BLOCK)
+    engine = LLMEngine.from_random(cfg, seed=0, config=EngineConfig(
+        block_size=BLOCK, num_blocks=BATCH * pages + 8 + PROMPT // BLOCK, max_num_seqs=BATCH, max_num_batched_tokens=PROMPT,
+        max_model_len=4096, enable_prefix_caching=False, dtype=torch.bfloat16, cuda_graphs=True))  # fmt: skip
+    runner, graphs, manager = engine.runner, engine.decode_graphs, engine.block_manager
+    generator = torch.Generator().manual_seed(1)
+
+    def prompt(n):
+        return torch.randint(0, size["vocab"], (n,), generator=generator).tolist()
+
+    def timed(function, repeats=3, warm=3):
+        times = []
+        for i in range(warm + repeats):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            function()
+            end.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(start.elapsed_time(end))
+        return statistics.median(times)
+
+    cache = manager.new_request()
+    assert manager.try_allocate(cache, PROMPT)
+    entry = StepEntry(cache, 0, prompt(PROMPT), (PROMPT - 1,))
+    prefill_ms = timed(lambda: runner.execute([entry]))
+    with KernelTimes() as kernel_times:
+        runner.execute([entry])
+    prompt_kernels = kernel_times.totals()
+    manager.free(cache)
+
+    caches = []
+    for _ in range(BATCH):
+        c = manager.new_request()
+        assert manager.try_allocate(c, CONTEXT + total_steps + 1)
+        runner.execute([StepEntry(c, 0, prompt(CONTEXT), ())])
+        caches.append(c)
+    tokens, position = prompt(BATCH), CONTEXT
+
+    def one_step(run):
+        nonlocal position
+        run([StepEntry(c, position, [tokens[i]], (0,)) for i, c in enumerate(caches)])
+        position += 1
+
+    for _ in range(warmup):
+        one_step(graphs.run)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step(graphs.run)
+    end.record()
+    torch.cuda.synchronize()
+    decode_ms = start.elapsed_time(end) / steps
+    one_step(runner.execute)  # an eager decode step first, so that its buffers exist
+    with KernelTimes() as kernel_times:
+        one_step(runner.execute)
+    decode_kernels = kernel_times.totals()
+    ops.raise_on_device_error()
+
+    layers = size["layers"]
+    bounds = rooflines(design, size, peaks)
+    kernels = {}
+    for phase, totals in (("prompt", prompt_kernels), ("decode", decode_kernels)):
+        for name, microseconds in sorted(totals.items()):
+            per_layer = microseconds / (layers if name not in ("embedding",) else 1)
+            record = {"us_per_layer": round(per_layer, 2)}
+            bound = bounds.get(f"{phase}.{name}")
+            if bound:
+                record["roofline_us"] = round(bound["roofline_us"], 3)
+                record["of_roofline"] = round(bound["roofline_us"] / per_layer, 4)
+            kernels[f"{phase}.{name}"] = record
+    return {
+        "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(PROMPT / prefill_ms * 1e3, 1),
+        "decode_ms_per_step": round(decode_ms, 4), "decode_tokens_per_s": round(BATCH / decode_ms * 1e3, 1),
+        "layer_weight_bytes": layer_weight_bytes(runner.model, layers), "kernels": kernels,
+    }  # fmt: skip
+
+
+def layer_weight_bytes(model, layers: int) -> int:
+    """Bytes of one layer's weights as the device holds them (matrices bfloat16, vectors float32)."""
+    import math
+
+    total = 0
+    for blk in model.blocks:
+        for spec in blk.weight_specs():
+            if spec.alias_of is None and not spec.optional:
+                total += math.prod(spec.shape) * (2 if spec.role == "matrix" else 4)
+    return total // layers
+
+
+def run(sizes: list[str], steps: int, warmup: int) -> dict:
+    import torch
+
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if peaks_file.is_file():
+        raw = json.loads(peaks_file.read_text())
+        peaks = {"hbm_gbs": float(raw.get("hbm_gbs", 6650.0)), "bf16_tflops": float(raw.get("bf16_tflops", 1590.0)), "source": "measured"}
+    out = {"metric": "prefill and decode throughput of Pimezen beside Qwen3 dense at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic", "workload": {"prompt_tokens": PROMPT, "decode_batch": BATCH, "decode_context": CONTEXT,
+                                             "window": WINDOW, "keep_first": KEEP_FIRST, "steps": steps, "warmup": warmup},
+           "peaks": peaks, "sizes": {}}  # fmt: skip
+    for name in sizes:
+        size = SIZES[name]
+        out["sizes"][name] = {"config": size}
+        for design, cfg in configs(size).items():
+            out["sizes"][name][design] = run_design(design, cfg, size, steps, warmup, peaks)
+            torch.cuda.empty_cache()
+    return out
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--sizes", default="1b,8b")
+    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--warmup", type=int, default=5)
+    args = parser.parse_args(argv)
+    print(json.dumps(run(args.sizes.split(","), args.steps, max(args.warmup, 3))))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
