@@ -159,19 +159,26 @@ def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dic
             function()
             end.record()
             torch.cuda.synchronize()
+            print(f"[design_bench]   iteration {i}: {start.elapsed_time(end):.2f} ms", file=sys.stderr, flush=True)
             if i >= warm:
                 times.append(start.elapsed_time(end))
         return statistics.median(times)
 
+    def note(text):
+        print(f"[design_bench] {design} width {size['width']}: {text}", file=sys.stderr, flush=True)
+
     cache = manager.new_request()
     assert manager.try_allocate(cache, PROMPT)
     entry = StepEntry(cache, 0, prompt(PROMPT), (PROMPT - 1,))
+    note("prompt step")
     prefill_ms = timed(lambda: runner.execute([entry]))
+    note(f"prompt step {prefill_ms:.2f} ms; kernels of a prompt step")
     with KernelTimes() as kernel_times:
         runner.execute([entry])
     prompt_kernels = kernel_times.totals()
     manager.free(cache)
 
+    note("filling the decode contexts")
     caches = []
     for _ in range(BATCH):
         c = manager.new_request()
@@ -185,6 +192,7 @@ def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dic
         run([StepEntry(c, position, [tokens[i]], (0,)) for i, c in enumerate(caches)])
         position += 1
 
+    note("decode steps")
     for _ in range(warmup):
         one_step(graphs.run)
     torch.cuda.synchronize()
@@ -195,6 +203,7 @@ def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dic
     end.record()
     torch.cuda.synchronize()
     decode_ms = start.elapsed_time(end) / steps
+    note(f"decode step {decode_ms:.3f} ms; kernels of a decode step")
     one_step(runner.execute)  # an eager decode step first, so that its buffers exist
     with KernelTimes() as kernel_times:
         one_step(runner.execute)

@@ -131,18 +131,261 @@ __global__ void __launch_bounds__(BIASED_WARPS * 32) biased_attention_kernel(Bia
     }
 }
 
+// ---- the same with 16-byte loads: head widths that are multiples of 8 (bfloat16) or 4 (float32)
+
+template <typename T>
+struct Packed;
+template <>
+struct Packed<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+    }
+};
+template <>
+struct Packed<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 x = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // a bfloat16 is the upper half of a float
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// One block of VEC_WARPS warps per (token, query head): 4 in float32 always (the same bits for a token in a
+// prompt and decoded alone), in bfloat16 1 when the step has items enough to fill the GPU and 8 when it has few.  Warp w takes the key tiles whose number (absolute
+// position / 32) is w modulo VEC_WARPS, keeps its own running maximum, denominator and sums, and warp 0 adds
+// the warps' results in ascending order: which warp visits which tile, and the order of every sum, depend on
+// the query's position only.  A lane owns NV segments of N consecutive value elements among the (value
+// heads x vdim) values of a key: segment u = lane + 32 * i is elements (u % per_row) * N .. of value head
+// u / per_row.  Values are fetched for four keys at a time, all loads ahead of the arithmetic.
+template <typename T, int NV, int VEC_WARPS>
+__global__ void __launch_bounds__(VEC_WARPS * 32) biased_attention_vec_kernel(BiasedArgs a) {
+    constexpr int N = Packed<T>::N;
+    extern __shared__ __align__(16) float vec_shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x / a.heads, head = blockIdx.x % a.heads;
+    const int d = a.dim, vd = a.vdim;
+    float* q = vec_shared;                                  // [dim]
+    float* part_stat = q + ((d + 3) / 4) * 4;               // [VEC_WARPS][2] maximum, denominator
+    float* part_acc = part_stat + VEC_WARPS * 2;            // [VEC_WARPS][NV][N][32]
+    pdl_trigger();
+    const float r1 = a.r1 ? a.r1[head] : 0.0f, r2 = a.r1 ? a.r2[head] : 0.0f;
+    pdl_wait();
+    const int own_kv = head / (a.heads / a.kv_heads);
+    const int first_value_head = a.spread ? 0 : own_kv;
+    const int value_heads = a.spread ? a.kv_heads : 1;
+    const int per_row = vd / N, segments = value_heads * per_row;
+    long long segment_offset[NV];  // where the lane's segments lie behind a key's first value head
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int u = lane + 32 * i;
+        segment_offset[i] = u < segments ? (static_cast<long long>(first_value_head + u / per_row) * a.page_size) * vd + (u % per_row) * N : -1;
+    }
+    const int position = a.positions[token];
+    const int* table = a.block_table + static_cast<size_t>(a.entry_of_token[token]) * a.table_width;
+    const T* k_pages = static_cast<const T*>(a.k_pages);
+    const T* v_pages = static_cast<const T*>(a.v_pages);
+
+    const T* q_src = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.heads + head) * d;
+    for (int i = threadIdx.x; i < d; i += VEC_WARPS * 32) q[i] = to_float(q_src[i]);
+    __syncthreads();
+
+    const int lowest = a.window > 0 ? max(position - a.window + 1, 0) : 0;
+    const int kept_end = a.window > 0 ? min(a.keep_first, lowest) : 0;
+    float running_max = -INFINITY, denom = 0.0f;
+    float acc[NV][N];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[i][e] = 0.0f;
+
+    for (int run = 0; run < 2; ++run) {
+        const int from = run == 0 ? 0 : lowest, to = run == 0 ? kept_end - 1 : position;  // inclusive
+        for (int tile = (from / 32) * 32; tile <= to; tile += 32) {
+            if ((tile >> 5) % VEC_WARPS != warp) continue;
+            const int key = tile + lane;
+            const bool valid = key >= from && key <= to;
+            int page = -1, offset = 0;
+            if (valid) {
+                page = table[key / a.page_size];
+                offset = key % a.page_size;
+            }
+            float score = -INFINITY;
+            if (page >= 0) {
+                const T* k_row = k_pages + ((static_cast<long long>(page) * a.kv_heads + own_kv) * a.page_size + offset) * d;
+                float dot = 0.0f;
+#pragma unroll 4
+                for (int i = 0; i < d; i += N) {
+                    float k[N];
+                    Packed<T>::load(k_row + i, k);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) dot = fmaf(q[i + e], k[e], dot);
+                }
+                score = dot * a.scale;
+                if (a.r1) score -= r1 * logf(1.0f + r2 * static_cast<float>(position - key));
+            }
+            const float new_max = fmaxf(running_max, warp_max(score));
+            if (new_max == -INFINITY) continue;  // nothing visible in this tile (uniform across the warp)
+            const float p = page >= 0 ? expf(score - new_max) : 0.0f;
+            const float rescale = expf(running_max - new_max);  // 0 on the warp's first tile (exp(-inf))
+            denom = denom * rescale + warp_sum(p);
+            running_max = new_max;
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[i][e] *= rescale;
+            // element offset of the key's value row in value head 0, -1 when masked
+            const long long row = page >= 0 ? (static_cast<long long>(page) * a.kv_heads * a.page_size + offset) * vd : -1;
+            // Values: for KEYS keys at a time, all loads ahead of the arithmetic.  One warp per item (a step
+            // with items enough to fill every SM) takes one key at a time: fewer registers, more warps per SM.
+            constexpr int KEYS = VEC_WARPS == 1 ? 1 : 4;
+#pragma unroll 4
+            for (int j0 = 0; j0 < 32; j0 += KEYS) {
+                float pj[KEYS];
+                long long rj[KEYS];
+                float v[KEYS][NV][N];
+#pragma unroll
+                for (int u = 0; u < KEYS; ++u) {
+                    pj[u] = __shfl_sync(0xffffffffu, p, j0 + u);
+                    rj[u] = __shfl_sync(0xffffffffu, row, j0 + u);
+                }
+#pragma unroll
+                for (int u = 0; u < KEYS; ++u)
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        if (rj[u] >= 0 && segment_offset[i] >= 0) {
+                            Packed<T>::load(v_pages + rj[u] + segment_offset[i], v[u][i]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < N; ++e) v[u][i][e] = 0.0f;  // a masked key has weight 0 as well
+                        }
+                    }
+#pragma unroll
+                for (int u = 0; u < KEYS; ++u)
+#pragma unroll
+                    for (int i = 0; i < NV; ++i)
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc[i][e] = fmaf(pj[u], v[u][i][e], acc[i][e]);
+            }
+        }
+    }
+    // The warps' partial results meet in shared memory; warp 0 adds them in ascending order.
+    if (lane == 0) {
+        part_stat[warp * 2] = running_max;
+        part_stat[warp * 2 + 1] = denom;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < N; ++e) part_acc[((warp * NV + i) * N + e) * 32 + lane] = acc[i][e];
+    __syncthreads();
+    if (warp != 0) return;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < VEC_WARPS; ++w) top = fmaxf(top, part_stat[w * 2]);
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[i][e] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < VEC_WARPS; ++w) {
+        const float m = part_stat[w * 2];
+        if (m == -INFINITY) continue;  // this warp saw no key
+        const float factor = expf(m - top);
+        total = fmaf(part_stat[w * 2 + 1], factor, total);
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[i][e] = fmaf(part_acc[((w * NV + i) * N + e) * 32 + lane], factor, acc[i][e]);
+    }
+    const float inv = 1.0f / total;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int u = lane + 32 * i;
+        if (u >= segments) continue;
+        const int c = u / per_row, e0 = (u % per_row) * N;
+        if (a.spread) {
+            float* out = static_cast<float*>(a.out) + ((static_cast<size_t>(token) * a.heads + head) * a.kv_heads + c) * vd + e0;
+#pragma unroll
+            for (int e = 0; e < N; ++e) out[e] = acc[i][e] * inv;
+        } else {
+            T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.heads + head) * vd + e0;
+#pragma unroll
+            for (int e = 0; e < N; ++e) out[e] = from_float<T>(acc[i][e] * inv);
+        }
+    }
+}
+
+template <typename T, int NV, int VEC_WARPS>
+static int launch_biased_vec_with(const BiasedArgs& a, cudaStream_t stream) {
+    static SharedMemoryOptIn opt_in;
+    constexpr int N = Packed<T>::N;
+    const size_t smem = (static_cast<size_t>((a.dim + 3) / 4) * 4 + VEC_WARPS * 2 + static_cast<size_t>(VEC_WARPS) * NV * N * 32) * sizeof(float);
+    if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        const int code = opt_in(biased_attention_vec_kernel<T, NV, VEC_WARPS>, static_cast<int>(smem));
+        if (code) return code;
+    }
+    const long long items = static_cast<long long>(a.tokens) * a.heads;
+    if (items > 0x7fffffffll) return ME_ERR_UNSUPPORTED;
+    return launch_kernel_in_order(biased_attention_vec_kernel<T, NV, VEC_WARPS>, static_cast<int>(items), VEC_WARPS * 32, smem, stream, a);
+}
+
+constexpr long long ITEMS_THAT_FILL_THE_GPU = 2048;
+
+template <typename T, int NV>
+static int launch_biased_vec_as(const BiasedArgs& a, cudaStream_t stream) {
+    if constexpr (sizeof(T) == 4) {
+        return launch_biased_vec_with<T, NV, 4>(a, stream);
+    } else {
+        if (static_cast<long long>(a.tokens) * a.heads >= ITEMS_THAT_FILL_THE_GPU) return launch_biased_vec_with<T, NV, 1>(a, stream);
+        return launch_biased_vec_with<T, NV, 8>(a, stream);
+    }
+}
+
+template <typename T>
+static int launch_biased_vec(const BiasedArgs& a, cudaStream_t stream, bool& taken) {
+    constexpr int N = Packed<T>::N;
+    const int segments = (a.spread ? a.kv_heads : 1) * (a.vdim / N);
+    const int per_lane = (segments + 31) / 32;
+    taken = true;
+    if (per_lane <= 1) return launch_biased_vec_as<T, 1>(a, stream);
+    if (per_lane <= 2) return launch_biased_vec_as<T, 2>(a, stream);
+    if (per_lane <= 4) return launch_biased_vec_as<T, 4>(a, stream);
+    if constexpr (N == 4) {
+        if (per_lane <= 8) return launch_biased_vec_as<T, 8>(a, stream);
+    }
+    taken = false;
+    return 0;
+}
+
 template <typename T>
 static int launch_biased(const BiasedArgs& a, cudaStream_t stream) {
+    // Which kernel runs depends on the model's sizes and the alignment of the engine's buffers only.
+    constexpr int N = Packed<T>::N;
+    const bool aligned = reinterpret_cast<uintptr_t>(a.k_pages) % 16 == 0 && reinterpret_cast<uintptr_t>(a.v_pages) % 16 == 0;
+    if (a.dim % N == 0 && a.vdim % N == 0 && aligned) {
+        bool taken = false;
+        const int code = launch_biased_vec<T>(a, stream, taken);
+        if (taken) return code;
+    }
     const int per_lane = (a.spread ? a.kv_heads : 1) * ((a.vdim + 31) / 32);
     const long long items = static_cast<long long>(a.tokens) * a.heads;
     const int blocks = static_cast<int>((items + BIASED_WARPS - 1) / BIASED_WARPS);
     const size_t smem = static_cast<size_t>(BIASED_WARPS) * a.dim * sizeof(float);
-    if (per_lane <= 2) return launch_kernel(biased_attention_kernel<T, 2>, blocks, BIASED_WARPS * 32, smem, stream, a);
-    if (per_lane <= 4) return launch_kernel(biased_attention_kernel<T, 4>, blocks, BIASED_WARPS * 32, smem, stream, a);
-    if (per_lane <= 8) return launch_kernel(biased_attention_kernel<T, 8>, blocks, BIASED_WARPS * 32, smem, stream, a);
-    if (per_lane <= 16) return launch_kernel(biased_attention_kernel<T, 16>, blocks, BIASED_WARPS * 32, smem, stream, a);
-    if (per_lane <= 32) return launch_kernel(biased_attention_kernel<T, 32>, blocks, BIASED_WARPS * 32, smem, stream, a);
-    if (per_lane <= 64) return launch_kernel(biased_attention_kernel<T, 64>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 2) return launch_kernel_in_order(biased_attention_kernel<T, 2>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 4) return launch_kernel_in_order(biased_attention_kernel<T, 4>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 8) return launch_kernel_in_order(biased_attention_kernel<T, 8>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 16) return launch_kernel_in_order(biased_attention_kernel<T, 16>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 32) return launch_kernel_in_order(biased_attention_kernel<T, 32>, blocks, BIASED_WARPS * 32, smem, stream, a);
+    if (per_lane <= 64) return launch_kernel_in_order(biased_attention_kernel<T, 64>, blocks, BIASED_WARPS * 32, smem, stream, a);
     return ME_ERR_UNSUPPORTED;
 }
 

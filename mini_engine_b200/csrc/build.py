@@ -43,6 +43,7 @@ LIBRARIES = {
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_programmatic_launch = True  # what every library is told when it is loaded, see set_programmatic_launch
 
 
 class BuildError(RuntimeError):
@@ -141,8 +142,23 @@ def compile_library(name: str, verbose: bool = True) -> Path:
 def load_library(name: str) -> ctypes.CDLL:
     with _lock:
         if name not in _loaded:
-            _loaded[name] = ctypes.CDLL(str(compile_library(name)))
+            library = ctypes.CDLL(str(compile_library(name)))
+            if hasattr(library, "me_set_programmatic_launch"):
+                library.me_set_programmatic_launch(ctypes.c_int(1 if _programmatic_launch else 0))
+            _loaded[name] = library
         return _loaded[name]
+
+
+def set_programmatic_launch(enabled: bool) -> bool:
+    """Tell every library (those loaded, and those loaded later) whether to launch its kernels as
+    programmatic dependents of their predecessors or in plain stream order.  Returns the old setting."""
+    global _programmatic_launch
+    with _lock:
+        previous, _programmatic_launch = _programmatic_launch, bool(enabled)
+        for library in _loaded.values():
+            if hasattr(library, "me_set_programmatic_launch"):
+                library.me_set_programmatic_launch(ctypes.c_int(1 if enabled else 0))
+    return previous
 
 
 def build_all(names: list[str] | None = None, verbose: bool = True) -> list[Path]:

@@ -65,6 +65,11 @@ struct SharedMemoryOptIn {
     }
 };
 
+// Whether this library's kernels are launched as programmatic dependents (the default) or in plain stream
+// order; the bindings set it per forward pass from what the model's parts say (every library has its own copy).
+static int g_programmatic_launch = 1;
+ME_EXPORT void me_set_programmatic_launch(int enabled) { g_programmatic_launch = enabled; }
+
 template <typename... KernelArgs, typename... Args>
 static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                 Args&&... args) {
@@ -78,5 +83,22 @@ static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 b
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
+    if (!g_programmatic_launch) config.numAttrs = 0;  // plain stream order: griddepcontrol.wait is then a no-op
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
+}
+
+// The same without the programmatic attribute: the kernel starts when everything before it in the stream
+// has completed.  For kernels that run for milliseconds (a scan over a whole prompt), behind which nothing
+// is gained by making the next kernels resident early.
+template <typename... KernelArgs, typename... Args>
+static inline int launch_kernel_in_order(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    config.attrs = nullptr;
+    config.numAttrs = 0;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
 }

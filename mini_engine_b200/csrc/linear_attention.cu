@@ -8,11 +8,10 @@
 // for the output projection.  The state of a request lives in its slot of the cache manager's state
 // array between steps; an entry that starts at position 0 starts from zero.
 //
-// Scan kernel: one warp per (entry, head, 32 value columns).  Each lane owns one column of the state in
-// registers ([dim] floats) and walks the entry's tokens in order; q, k and alpha of a chunk of tokens are
-// prepared by the whole warp in shared memory first (the sum of the product's partial sums, the query
-// scale, the decay from the low-rank sums in 32-bit), so the serial part is two multiply-adds per state
-// element and token.  Columns are independent, hence the result does not depend on how the work is cut
+// Prepare kernel: for all tokens at once, the sum of the product's partial sums, the query scale and the
+// decay from the low-rank sums, in 32-bit.  Scan kernel: one warp per (entry, head, 32 value columns).  Each
+// lane owns one column of the state in registers ([dim] floats) and walks the entry's tokens in order, so
+// the serial part is two multiply-adds per state element and token.  Columns are independent, hence the result does not depend on how the work is cut
 // over warps, and a token's output depends on the tokens before it only through the state: the bits are
 // the same for a whole prompt, its portions and single decoded tokens.
 //
@@ -21,42 +20,119 @@
 
 #include <algorithm>
 
-struct ScanArgs {
-    const float* proj;  // [splits][tokens][width] partial sums of the fused input projection
-    int splits;
-    size_t split_stride;
-    int width;                      // columns of a row of proj
-    int q_col, k_col, v_col, a_col;  // first column of q [heads*dim], k [heads*dim], v [heads*vdim], low-rank [rank]
-    const float* a2;       // [heads*dim][rank]
-    const float* a2_bias;  // [heads*dim]
-    const int* cu_tokens;   // [entries + 1]
-    const int* state_slots; // [entries]
-    const int* fresh;       // [entries] 1: the entry starts its request, the state starts at zero
-    float* state;           // [slots + 1][heads][dim][vdim]
-    float* out;             // [tokens][heads][vdim] float32: o_t before the norm
-    float q_scale, inv_tau;
-    int heads, dim, vdim, rank;
-};
-
-constexpr int SCAN_CHUNK = 16;
-
 // log(sigmoid(z)) without overflow: -softplus(-z).
 __device__ __forceinline__ float log_sigmoid(float z) {
     return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
 }
 
+// ------------------------------------------------------------------------------- prepare
+
+// For every token, head and key channel: q (scaled), k and the decay, float32, as
+// prepared[token][head][0..2][dim].  A block takes PREP_TOKENS tokens, so that a row of the decay's
+// second factor (stored transposed, [rank][heads*dim]) is read once for all of them.
+struct PrepArgs {
+    const float* proj;  // [splits][tokens][width] partial sums of the fused input projection
+    int splits;
+    size_t split_stride;
+    int width;
+    int q_col, k_col, a_col;  // first column of q [heads*dim], k [heads*dim], low-rank sums [rank]
+    const float* a2t;         // [rank][heads*dim]
+    const float* a2_bias;     // [heads*dim]
+    float* prepared;          // [tokens][heads][3][dim]
+    float q_scale, inv_tau;
+    int tokens, heads, dim, rank;
+};
+
+constexpr int PREP_TOKENS = 8;
+
+__global__ void __launch_bounds__(256) gla_prepare_kernel(PrepArgs a) {
+    extern __shared__ float low[];  // [PREP_TOKENS][rank]
+    const int first = blockIdx.x * PREP_TOKENS;
+    const int count = min(PREP_TOKENS, a.tokens - first);
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < count * a.rank; i += blockDim.x) {
+        const int t = i / a.rank, r = i % a.rank;
+        const float* src = a.proj + static_cast<size_t>(first + t) * a.width + a.a_col + r;
+        float sum = 0.0f;
+        for (int p = 0; p < a.splits; ++p) sum += src[p * a.split_stride];
+        low[i] = sum;
+    }
+    __syncthreads();
+    const int items = a.heads * a.dim;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < items; i += gridDim.y * blockDim.x) {
+        float z[PREP_TOKENS];
+#pragma unroll
+        for (int t = 0; t < PREP_TOKENS; ++t) z[t] = 0.0f;
+        for (int r = 0; r < a.rank; ++r) {
+            const float w = a.a2t[static_cast<size_t>(r) * items + i];
+#pragma unroll
+            for (int t = 0; t < PREP_TOKENS; ++t)
+                if (t < count) z[t] = fmaf(w, low[t * a.rank + r], z[t]);
+        }
+        const float bias = a.a2_bias[i];
+        const int head = i / a.dim, d = i % a.dim;
+#pragma unroll
+        for (int t = 0; t < PREP_TOKENS; ++t) {
+            if (t >= count) break;
+            const float* row = a.proj + static_cast<size_t>(first + t) * a.width + i;
+            float q = 0.0f, k = 0.0f;
+            for (int p = 0; p < a.splits; ++p) {
+                q += row[p * a.split_stride + a.q_col];
+                k += row[p * a.split_stride + a.k_col];
+            }
+            float* dst = a.prepared + ((static_cast<size_t>(first + t) * a.heads + head) * 3) * a.dim + d;
+            dst[0] = q * a.q_scale;
+            dst[a.dim] = k;
+            dst[2 * a.dim] = expf(log_sigmoid(z[t] + bias) * a.inv_tau);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- scan
+
+struct ScanArgs {
+    const float* proj;  // [splits][tokens][width]: the value columns are read from here
+    int splits;
+    size_t split_stride;
+    int width;
+    int v_col;               // first column of v [heads*vdim]
+    const float* prepared;   // [tokens][heads][3][dim] from the prepare kernel
+    const int* cu_tokens;    // [entries + 1]
+    const int* state_slots;  // [entries]
+    const int* fresh;        // [entries] 1: the entry starts its request, the state starts at zero
+    float* state;            // [slots + 1][heads][dim][vdim]
+    float* out;              // [tokens][heads][vdim] float32: o_t before the norm
+    int heads, dim, vdim;
+};
+
+constexpr int SCAN_CHUNK = 16;
+
+__device__ __forceinline__ void copy_async_16(float* shared_dst, const float* global_src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global_src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory"); }
+
+// One warp per (entry, head, 32 value columns); a lane keeps its column of the state in registers.
+// q, k and decay of the next chunk of tokens arrive in shared memory (asynchronous copies, two buffers)
+// and its values in registers while the current chunk is computed.
 template <int DIMP>  // dim rounded up: the registers a lane holds of its state column
 __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
-    extern __shared__ float staged[];
-    float* q_s = staged;                          // [SCAN_CHUNK][DIMP]
-    float* k_s = q_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][DIMP]
-    float* d_s = k_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][DIMP] decay
-    float* v_s = d_s + SCAN_CHUNK * DIMP;         // [SCAN_CHUNK][32] this warp's value columns
-    float* r_s = v_s + SCAN_CHUNK * 32;           // [SCAN_CHUNK][rank] low-rank sums
+    extern __shared__ __align__(16) float staged[];
+    constexpr int TILE = SCAN_CHUNK * 3 * DIMP;
+    float* tiles = staged;              // [2][SCAN_CHUNK][3][DIMP]
+    float* v_s = staged + 2 * TILE;     // [2][SCAN_CHUNK][32] this warp's value columns
     const int entry = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int column = blockIdx.z * 32 + lane;
     const bool live = column < a.vdim;
     const int dim = a.dim;
+    const bool vector = dim % 4 == 0;
+    for (int i = lane; i < 2 * SCAN_CHUNK * 3 * (DIMP - dim); i += 32)  // channels dim..DIMP are zero for good
+        tiles[(i / (DIMP - dim)) * DIMP + dim + i % (DIMP - dim)] = 0.0f;
+    __syncwarp();
     pdl_trigger();
     pdl_wait();
     const int begin = a.cu_tokens[entry], end = a.cu_tokens[entry + 1];
@@ -67,50 +143,64 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
 #pragma unroll
     for (int d = 0; d < DIMP; ++d) s[d] = (live && !from_zero && d < dim) ? state[static_cast<size_t>(d) * a.vdim] : 0.0f;
 
-    for (int chunk = begin; chunk < end; chunk += SCAN_CHUNK) {
+    auto stage_tile = [&](int chunk, int buffer) {  // q, k, decay of tokens chunk .. chunk + count
         const int count = min(SCAN_CHUNK, end - chunk);
-        __syncwarp();
-        for (int i = lane; i < count * a.rank; i += 32) {
-            const int t = i / a.rank, r = i % a.rank;
-            const float* src = a.proj + static_cast<size_t>(chunk + t) * a.width + a.a_col + r;
-            float sum = 0.0f;
-            for (int p = 0; p < a.splits; ++p) sum += src[p * a.split_stride];
-            r_s[t * a.rank + r] = sum;
-        }
-        __syncwarp();
-        for (int i = lane; i < count * DIMP; i += 32) {
-            const int t = i / DIMP, d = i % DIMP;
-            float q = 0.0f, k = 0.0f, decay = 0.0f;
-            if (d < dim) {
-                const float* row = a.proj + static_cast<size_t>(chunk + t) * a.width + head * dim + d;
-                for (int p = 0; p < a.splits; ++p) {
-                    q += row[p * a.split_stride + a.q_col];
-                    k += row[p * a.split_stride + a.k_col];
-                }
-                q *= a.q_scale;
-                const float* w = a.a2 + static_cast<size_t>(head * dim + d) * a.rank;
-                float z = 0.0f;
-                for (int r = 0; r < a.rank; ++r) z = fmaf(w[r], r_s[t * a.rank + r], z);
-                z += a.a2_bias[head * dim + d];
-                decay = expf(log_sigmoid(z) * a.inv_tau);
+        float* tile = tiles + buffer * TILE;
+        if (vector) {
+            const int quads = 3 * dim / 4;
+            for (int i = lane; i < count * quads; i += 32) {
+                const int t = i / quads, j = (i % quads) * 4;
+                const int which = j / dim, d = j % dim;
+                copy_async_16(tile + (t * 3 + which) * DIMP + d,
+                              a.prepared + ((static_cast<size_t>(chunk + t) * a.heads + head) * 3) * dim + j);
             }
-            q_s[i] = q, k_s[i] = k, d_s[i] = decay;
+        } else {
+            for (int i = lane; i < count * 3 * dim; i += 32) {
+                const int t = i / (3 * dim), j = i % (3 * dim);
+                tile[(t * 3 + j / dim) * DIMP + j % dim] = a.prepared[((static_cast<size_t>(chunk + t) * a.heads + head) * 3) * dim + j];
+            }
         }
-        for (int t = 0; t < count; ++t) {
-            float value = 0.0f;
-            if (live) {
+        copy_async_commit();
+    };
+    auto load_values = [&](int chunk, float (&v)[SCAN_CHUNK]) {
+        const int count = min(SCAN_CHUNK, end - chunk);
+#pragma unroll
+        for (int t = 0; t < SCAN_CHUNK; ++t) {
+            v[t] = 0.0f;
+            if (live && t < count) {
                 const float* src = a.proj + static_cast<size_t>(chunk + t) * a.width + a.v_col + head * a.vdim + column;
-                for (int p = 0; p < a.splits; ++p) value += src[p * a.split_stride];
+                for (int p = 0; p < a.splits; ++p) v[t] += src[p * a.split_stride];
             }
-            v_s[t * 32 + lane] = value;
+        }
+    };
+
+    float v_next[SCAN_CHUNK];
+    if (begin < end) {
+        stage_tile(begin, 0);
+        load_values(begin, v_next);
+#pragma unroll
+        for (int t = 0; t < SCAN_CHUNK; ++t) v_s[t * 32 + lane] = v_next[t];
+    }
+    int buffer = 0;
+    for (int chunk = begin; chunk < end; chunk += SCAN_CHUNK, buffer ^= 1) {
+        const int count = min(SCAN_CHUNK, end - chunk);
+        const bool more = chunk + SCAN_CHUNK < end;
+        if (more) {
+            stage_tile(chunk + SCAN_CHUNK, buffer ^ 1);
+            load_values(chunk + SCAN_CHUNK, v_next);
+            copy_async_wait<1>();
+        } else {
+            copy_async_wait<0>();
         }
         __syncwarp();
+        const float* tile = tiles + buffer * TILE;
+        const float* values = v_s + buffer * SCAN_CHUNK * 32;
 #pragma unroll 1
         for (int t = 0; t < count; ++t) {
-            const float v = v_s[t * 32 + lane];
-            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * DIMP);
-            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * DIMP);
-            const float4* d4 = reinterpret_cast<const float4*>(d_s + t * DIMP);
+            const float v = values[t * 32 + lane];
+            const float4* q4 = reinterpret_cast<const float4*>(tile + (t * 3 + 0) * DIMP);
+            const float4* k4 = reinterpret_cast<const float4*>(tile + (t * 3 + 1) * DIMP);
+            const float4* d4 = reinterpret_cast<const float4*>(tile + (t * 3 + 2) * DIMP);
             float o = 0.0f;
 #pragma unroll
             for (int d = 0; d < DIMP; d += 4) {
@@ -126,6 +216,11 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
             }
             if (live) a.out[(static_cast<size_t>(chunk + t) * a.heads + head) * a.vdim + column] = o;
         }
+        __syncwarp();
+        if (more) {
+#pragma unroll
+            for (int t = 0; t < SCAN_CHUNK; ++t) v_s[(buffer ^ 1) * SCAN_CHUNK * 32 + t * 32 + lane] = v_next[t];
+        }
     }
     if (live) {
 #pragma unroll
@@ -137,24 +232,36 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
 template <int DIMP>
 static int launch_scan(const ScanArgs& a, int entries, cudaStream_t stream) {
     static SharedMemoryOptIn opt_in;
-    const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (3 * DIMP + 32 + a.rank)) * sizeof(float);
+    const size_t smem = (static_cast<size_t>(2) * SCAN_CHUNK * (3 * DIMP + 32)) * sizeof(float);
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
     if (smem > 48 * 1024) {
         const int code = opt_in(gla_scan_kernel<DIMP>, static_cast<int>(smem));
         if (code) return code;
     }
     const dim3 grid(entries, a.heads, (a.vdim + 31) / 32);
-    return launch_kernel(gla_scan_kernel<DIMP>, grid, 32, smem, stream, a);
+    return launch_kernel_in_order(gla_scan_kernel<DIMP>, grid, 32, smem, stream, a);
 }
 
+// Both kernels, one after the other: `prepared` is scratch of tokens * heads * 3 * dim floats, `a2t` the
+// decay's second factor transposed to [rank][heads*dim].
 ME_EXPORT int me_gla_scan(const float* proj, int splits, long long split_stride, int width, int q_col, int k_col,
-                          int v_col, int a_col, const float* a2, const float* a2_bias, const int* cu_tokens,
-                          const int* state_slots, const int* fresh, float* state, float* out, float q_scale,
-                          float tau, int entries, int heads, int dim, int vdim, int rank, cudaStream_t stream) {
-    if (entries <= 0) return 0;
+                          int v_col, int a_col, const float* a2t, const float* a2_bias, const int* cu_tokens,
+                          const int* state_slots, const int* fresh, float* state, float* out, float* prepared,
+                          float q_scale, float tau, int tokens, int entries, int heads, int dim, int vdim, int rank,
+                          cudaStream_t stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
     if (dim < 1 || vdim < 1 || rank < 1 || heads < 1 || !(tau > 0.0f)) return ME_ERR_ARGUMENT;
-    ScanArgs a{proj, splits, static_cast<size_t>(split_stride), width, q_col, k_col, v_col, a_col, a2, a2_bias,
-               cu_tokens, state_slots, fresh, state, out, q_scale, 1.0f / tau, heads, dim, vdim, rank};
+    if (static_cast<size_t>(PREP_TOKENS) * rank * sizeof(float) > 48 * 1024) return ME_ERR_UNSUPPORTED;
+    PrepArgs p{proj, splits, static_cast<size_t>(split_stride), width, q_col, k_col, a_col, a2t, a2_bias, prepared,
+               q_scale, 1.0f / tau, tokens, heads, dim, rank};
+    // Few tokens: the channels of a token block are spread over several blocks as well.
+    const int token_blocks = (tokens + PREP_TOKENS - 1) / PREP_TOKENS;
+    const int channel_blocks = token_blocks >= 148 ? 1 : std::min((heads * dim + 255) / 256, 16);
+    const int code = launch_kernel(gla_prepare_kernel, dim3(token_blocks, channel_blocks), 256,
+                                   static_cast<size_t>(PREP_TOKENS) * rank * sizeof(float), stream, p);
+    if (code) return code;
+    ScanArgs a{proj, splits, static_cast<size_t>(split_stride), width, v_col, prepared, cu_tokens, state_slots,
+               fresh, state, out, heads, dim, vdim};
     if (dim <= 16) return launch_scan<16>(a, entries, stream);
     if (dim <= 32) return launch_scan<32>(a, entries, stream);
     if (dim <= 64) return launch_scan<64>(a, entries, stream);

@@ -62,6 +62,25 @@ class stream_scope:
         _scoped_stream = self.previous
 
 
+class programmatic_launch:
+    """While open, the package's kernels are launched as programmatic dependents of their predecessors
+    (``True``, the default outside any scope) or in plain stream order (``False``).  The model's forward
+    pass opens one with what its parts say."""
+
+    def __init__(self, enabled: bool):
+        self.enabled = bool(enabled)
+
+    def __enter__(self) -> None:
+        from mini_engine_b200.csrc.build import set_programmatic_launch
+
+        self.previous = set_programmatic_launch(self.enabled)
+
+    def __exit__(self, *exc) -> None:
+        from mini_engine_b200.csrc.build import set_programmatic_launch
+
+        set_programmatic_launch(self.previous)
+
+
 class _Counter:
     """Kernel launches issued through this package's bindings since import."""
 
@@ -460,26 +479,30 @@ def branch_sum(branches: list[tuple[torch.Tensor, float]], out: torch.Tensor) ->
 
 
 def gla_scan(
-    *, proj: torch.Tensor, columns: dict[str, int], a2: torch.Tensor, a2_bias: torch.Tensor, ctx, state: torch.Tensor,
-    out: torch.Tensor, q_scale: float, tau: float, heads: int, dim: int, vdim: int,
+    *, proj: torch.Tensor, columns: dict[str, int], a2t: torch.Tensor, a2_bias: torch.Tensor, ctx, state: torch.Tensor,
+    out: torch.Tensor, prepared: torch.Tensor, q_scale: float, tau: float, heads: int, dim: int, vdim: int,
 ) -> None:  # fmt: skip
     """The recurrence of gated linear attention over the batch's tokens, entry by entry, from and
     into each request's state slot.  ``proj`` is ``[S, T, width]`` float32 partial sums whose
-    ``columns`` ``q, k, v, a`` say where each projection starts; ``out`` is float32 ``[T, heads, vdim]``."""
-    _need(proj, torch.float32, "proj"), _need(a2, torch.float32, "a2"), _need(a2_bias, torch.float32, "a2_bias")
-    _need(state, torch.float32, "state"), _need(out, torch.float32, "out")
-    rank = a2.shape[1]
-    if a2.shape != (heads * dim, rank) or a2_bias.shape != (heads * dim,) or state.shape[1:] != (heads, dim, vdim):
+    ``columns`` ``q, k, v, a`` say where each projection starts; ``a2t`` is the decay's second factor
+    transposed, ``[rank, heads * dim]``; ``out`` is float32 ``[T, heads, vdim]``; ``prepared`` is float32
+    scratch of ``T * heads * 3 * dim`` values (q, k and decay of every token, made by a first kernel)."""
+    _need(proj, torch.float32, "proj"), _need(a2t, torch.float32, "a2t"), _need(a2_bias, torch.float32, "a2_bias")
+    _need(state, torch.float32, "state"), _need(out, torch.float32, "out"), _need(prepared, torch.float32, "prepared")
+    rank, tokens = a2t.shape[0], proj.shape[1]
+    if a2t.shape != (rank, heads * dim) or a2_bias.shape != (heads * dim,) or state.shape[1:] != (heads, dim, vdim):
         raise KernelError("gla_scan: decay weights or state do not fit heads/dim/vdim")
+    if prepared.numel() < tokens * heads * 3 * dim or out.numel() < tokens * heads * vdim:
+        raise KernelError("gla_scan: scratch or output too small")
     fn = _fn(
         "linear_attention",
         "me_gla_scan",
-        [c_void_p, c_int, c_longlong] + [c_int] * 5 + [c_void_p] * 7 + [c_float, c_float] + [c_int] * 5 + [c_void_p],
+        [c_void_p, c_int, c_longlong] + [c_int] * 5 + [c_void_p] * 8 + [c_float, c_float] + [c_int] * 6 + [c_void_p],
     )
     code = fn(
         _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], columns["q"], columns["k"], columns["v"], columns["a"],
-        _ptr(a2), _ptr(a2_bias), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(state), _ptr(out),
-        float(q_scale), float(tau), ctx.num_entries, heads, dim, vdim, rank, _stream(),
+        _ptr(a2t), _ptr(a2_bias), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(state), _ptr(out),
+        _ptr(prepared), float(q_scale), float(tau), tokens, ctx.num_entries, heads, dim, vdim, rank, _stream(),
     )  # fmt: skip
     _check(code, "gla_scan")
 

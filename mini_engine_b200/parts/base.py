@@ -153,6 +153,10 @@ class Part:
     # alone, so that a step of a fixed token count can be captured in a CUDA graph and replayed for
     # other requests (a part whose Python reads ``ctx.host`` or branches on values must say False).
     capturable = False
+    # Whether a step of a model with this part may launch its kernels as programmatic dependents of one
+    # another (CTAs of a kernel resident while its predecessor still runs).  A part says False when steps
+    # with its kernels were seen to stall that way; the whole step then runs in plain stream order.
+    programmatic_launch = True
 
     def weight_specs(self) -> list[WeightSpec]:
         return []

@@ -13,7 +13,8 @@ token in the request's state slot of the cache manager; the decay (sigmoid, its 
 the recurrence and the unit norm are computed in 32-bit from the 32-bit sums of the projections.
 
 The five projections of the input run as one product on the row-concatenated weight; the second,
-small factor of the decay's low-rank projection is applied inside the scan kernel.
+small factor of the decay's low-rank projection is applied by the kernel that prepares q, k and the
+decays of all tokens for the scan.
 """
 
 from __future__ import annotations
@@ -31,6 +32,10 @@ from mini_engine_b200.weights.loader import WeightSpec
 @register("mixer", "gated_linear_attention")
 class GatedLinearAttention(Mixer):
     capturable = True
+    # Prompt steps of a model with this mixer at widths of 4,096 stalled on a B200 while their kernels were
+    # launched as programmatic dependents (seven 2,048-token steps in a row, every time) and ran through in
+    # plain stream order; which kernels meet badly is not known, so such a model's steps run in order.
+    programmatic_launch = False
 
     def __init__(
         self,
@@ -64,7 +69,7 @@ class GatedLinearAttention(Mixer):
             column += width
         self.proj: Linear | None = None
         self.out: Linear | None = None
-        self.norm_weight = self.a2 = self.a2_bias = None
+        self.norm_weight = self.a2t = self.a2_bias = None
 
     def state(self) -> StateSpec:
         return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
@@ -88,15 +93,17 @@ class GatedLinearAttention(Mixer):
         n = self.names
         self.proj = Linear(torch.cat([tensors[n[key]] for key in ("q", "k", "v", "g", "a1")], dim=0).contiguous())
         self.out = Linear(tensors[n["o"]])
-        self.norm_weight, self.a2, self.a2_bias = tensors[n["norm"]], tensors[n["a2"]], tensors[n["a2_bias"]]
+        self.norm_weight, self.a2_bias = tensors[n["norm"]], tensors[n["a2_bias"]]
+        self.a2t = tensors[n["a2"]].t().contiguous()  # [rank, heads * dim]: the prepare kernel reads it along the channels
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         tokens = h.shape[0]
         proj = self.proj.forward(h, ctx, "gla.proj")
         raw = ctx.buffer("gla.raw", (tokens, self.heads * self.vdim), torch.float32)
+        prepared = ctx.buffer("gla.prepared", (tokens, self.heads * 3 * self.dim), torch.float32)
         ops.gla_scan(
-            proj=proj, columns=self.columns, a2=self.a2, a2_bias=self.a2_bias, ctx=ctx, state=cache.state, out=raw,
-            q_scale=self.q_scale, tau=self.tau, heads=self.heads, dim=self.dim, vdim=self.vdim,
+            proj=proj, columns=self.columns, a2t=self.a2t, a2_bias=self.a2_bias, ctx=ctx, state=cache.state, out=raw,
+            prepared=prepared, q_scale=self.q_scale, tau=self.tau, heads=self.heads, dim=self.dim, vdim=self.vdim,
         )  # fmt: skip
         gated = ctx.buffer("gla.out", (tokens, self.heads * self.vdim), ctx.dtype)
         ops.gla_finish(

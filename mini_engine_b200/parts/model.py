@@ -78,6 +78,14 @@ class DecoderModel:
                 parts.append(position)
         return all(getattr(part, "capturable", False) for part in parts)
 
+    @property
+    def programmatic_launch(self) -> bool:
+        """Whether every part agrees to programmatic dependent launches (see ``Part.programmatic_launch``)."""
+        parts = [self.embedding, self.final_norm, self.head]
+        for blk in self.blocks:
+            parts += [blk, *blk.parts()]
+        return all(getattr(part, "programmatic_launch", True) for part in parts)
+
     def cache_needs(self) -> list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]]:
         """For every entry of the execution order: its per-token need, its per-request
         need, and the earlier entry whose cache it reads instead (or ``None``)."""
@@ -99,7 +107,7 @@ class DecoderModel:
     def forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:
         """Run the batch's tokens through every entry of the order; return float32 logits
         ``[N, vocab]`` at ``logits_rows`` (int32 row numbers among the batch's tokens)."""
-        with ops.stream_scope():
+        with ops.stream_scope(), ops.programmatic_launch(self.programmatic_launch):
             return self._forward(ctx, caches, logits_rows)
 
     def _forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:

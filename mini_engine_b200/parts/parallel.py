@@ -39,6 +39,10 @@ class ParallelMixers(Mixer):
     def capturable(self) -> bool:  # type: ignore[override]
         return all(getattr(branch, "capturable", False) for branch in self.branches)
 
+    @property
+    def programmatic_launch(self) -> bool:  # type: ignore[override]
+        return all(getattr(branch, "programmatic_launch", True) for branch in self.branches)
+
     def paged_cache(self) -> PagedCacheSpec | None:
         return next((b.paged_cache() for b in self.branches if b.paged_cache() is not None), None)
 

@@ -299,9 +299,10 @@ def scan(proj_parts, columns, a2, bias, state, counts, slots, fresh, heads, dim,
 
     tokens = proj_parts.shape[1]
     out = torch.empty(tokens, heads * vdim, dtype=torch.float32, device="cuda")
-    ops.gla_scan(proj=proj_parts.cuda().contiguous(), columns=columns, a2=a2.cuda(), a2_bias=bias.cuda(),
-                 ctx=FakeContext(counts, slots, fresh), state=state, out=out, q_scale=dim**-0.5, tau=tau, heads=heads,
-                 dim=dim, vdim=vdim)  # fmt: skip
+    prepared = torch.empty(tokens, heads * 3 * dim, dtype=torch.float32, device="cuda")
+    ops.gla_scan(proj=proj_parts.cuda().contiguous(), columns=columns, a2t=a2.t().contiguous().cuda(), a2_bias=bias.cuda(),
+                 ctx=FakeContext(counts, slots, fresh), state=state, out=out, prepared=prepared, q_scale=dim**-0.5,
+                 tau=tau, heads=heads, dim=dim, vdim=vdim)  # fmt: skip
     torch.cuda.synchronize()
     return out.cpu().view(tokens, heads, vdim)
 
