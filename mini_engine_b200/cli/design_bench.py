@@ -46,7 +46,7 @@ def configs(size: dict):
         "mixer": {
             "left": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["head_dim"], "vdim": size["head_dim"],
                      "scale": size["head_dim"] ** -0.5, "mask": {"size": WINDOW, "keep_first": KEEP_FIRST}},
-            "right": {"heads": size["heads"], "dim": size["lin_dim"], "vdim": size["lin_vdim"], "tau": 16.0, "decay_rank": size["rank"]},
+            "right": {"heads": size["heads"], "dim": size["lin_dim"], "vdim": size["lin_vdim"], "tau": 8.0, "decay_rank": size["rank"]},
             "left_scale": 1.0, "right_scale": 1.0,
         },
         "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0},

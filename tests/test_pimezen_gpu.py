@@ -22,7 +22,7 @@ pytestmark = pytest.mark.gpu
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # Largest |engine - plain| relative to the request's largest |logit|: float32 sums in another order;
 # bfloat16 activations rounded between kernels (weights are compared as rounded to bfloat16).
-TOLERANCE = {"float32": 1e-5, "bfloat16": 2.5e-2}  # about twice the worst that any test of this file reaches on a B200
+TOLERANCE = {"float32": 1e-5, "bfloat16": 4e-2}  # about twice the worst that any test of this file reaches on a B200 (1.7e-6, 2.0e-2)
 
 
 def branch(heads, kv_heads, dim, vdim, scale, window, keep_first):
@@ -44,7 +44,7 @@ CONFIG_P = {
         layer(branch(4, 2, 16, 8, 0.3, 12, 3), {"heads": 2, "dim": 8, "vdim": 24, "tau": 4.0, "decay_rank": 4}, 0.6, 1.3,
               {"kind": "dense", "ff": 56, "limit": 1.5}),
         layer(branch(3, 3, 24, 40, 0.21, 7, 0), {"heads": 3, "dim": 18, "vdim": 33, "tau": 9.0, "decay_rank": 3}, 1.2, 0.7, None),
-        layer(branch(4, 1, 16, 16, 0.25, 400, 5), {"heads": 1, "dim": 32, "vdim": 64, "tau": 2.5, "decay_rank": 6}, 0.9, 1.0,
+        layer(branch(4, 1, 16, 16, 0.25, 400, 5), {"heads": 1, "dim": 36, "vdim": 96, "tau": 2.5, "decay_rank": 6}, 0.9, 1.0,
               {"kind": "dense", "ff": 24, "limit": 0.7}),
     ],
 }  # fmt: skip
@@ -58,7 +58,19 @@ CONFIG_Q = {
               {"kind": "dense", "ff": 72, "limit": 1.0}),
     ],
 }  # fmt: skip
-CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q}
+# Sizes that no fast path takes: a width that is no multiple of 8 (bfloat16 products on CUDA cores), head widths
+# that are no multiples of 8 or of 4 (the scalar attention kernel in bfloat16, in the second layer in float32
+# too), one head and one KV head, a feed-forward narrower than the model, a window of one token.
+CONFIG_R = {
+    "architecture": "Pimezen", "vocab": 51, "width": 36, "norm": {"eps": 1e-4},
+    "layers": [
+        layer(branch(2, 1, 12, 20, 0.4, 9, 2), {"heads": 3, "dim": 5, "vdim": 7, "tau": 3.0, "decay_rank": 1}, 1.5, 0.5,
+              {"kind": "dense", "ff": 17, "limit": 0.9}),
+        layer(branch(1, 1, 10, 6, 0.3, 1, 4), {"heads": 2, "dim": 6, "vdim": 10, "tau": 20.0, "decay_rank": 9}, 0.7, 1.4,
+              {"kind": "dense", "ff": 64, "limit": 5.0}),
+    ],
+}  # fmt: skip
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R}
 
 
 def random_ids(seed, count, vocab):
@@ -123,7 +135,7 @@ def compare(got, expected, requests, dtype_name):
     note_error("pimezen " + dtype_name, worst)
 
 
-LENGTHS = {"P": [70, 45, 133, 9, 97, 33, 1, 2], "Q": [150, 64, 17, 81, 49, 130]}
+LENGTHS = {"P": [70, 45, 133, 9, 97, 33, 1, 2], "Q": [150, 64, 17, 81, 49, 130], "R": [40, 3, 77, 18, 1, 60]}
 
 
 def requests_for(name):
@@ -134,7 +146,7 @@ def requests_for(name):
 
 
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
 @pytest.mark.parametrize("schedule", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
 def test_schedules_match_plain(name, dtype_name, schedule, folders):
     """Whole prompts; the last 32 tokens one by one (the windows pass over decoded tokens); portions down
@@ -182,6 +194,36 @@ def test_a_slot_that_is_used_again_starts_from_zero(folders):
     second = replayer.step({"step": 2, "entries": [{"id": "b", "tokens": b[20:], "want": [16]}], "end": ["b"]})
     alone = Replayer(folders["P"], torch.float32, 64, 16).step({"step": 0, "entries": [{"id": "b", "tokens": b, "want": [36]}], "end": ["b"]})
     assert slot_pages and torch.equal(second, alone) and not torch.equal(first, alone)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_the_replay_program_itself(folders, dtype_name, tmp_path):
+    """`bin/trace_run` as a process on a model folder of this design: mixed steps in, `done` lines and logit
+    files out, equal to the plain implementation."""
+    import subprocess
+    import sys
+
+    import numpy as np
+    from conftest import ROOT
+
+    requests = requests_for("R")
+    steps = schedules.mixed(requests)
+    out = tmp_path / "out"
+    feed = "".join(json.dumps(record) + "\n" for record in steps)
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folders["R"]), "--dtype", dtype_name,
+         "--out", str(out), "--max-tokens", str(schedules.peak_live_tokens(steps))],
+        input=feed, capture_output=True, text=True, timeout=900,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [line for line in proc.stdout.splitlines() if line.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    outputs = {}
+    for record in steps:
+        wanted = sum(len(e.get("want", [])) for e in record["entries"])
+        if wanted:
+            data = np.fromfile(out / f"{record['step']}.f32", dtype="<f4")
+            outputs[record["step"]] = torch.from_numpy(data.reshape(wanted, CONFIG_R["vocab"]).copy())
+    compare(schedules.collect(steps, outputs), expected_logits(folders["R"], requests), requests, dtype_name)
 
 
 # ---------------------------------------------------------------------- mechanisms alone: attention
