@@ -158,7 +158,7 @@ struct Packed<__nv_bfloat16> {
 };
 
 // One block of VEC_WARPS warps per (token, query head): 4 in float32 always (the same bits for a token in a
-// prompt and decoded alone), in bfloat16 1 when the step has items enough to fill the GPU and 8 when it has few.  Warp w takes the key tiles whose number (absolute
+// prompt and decoded alone), in bfloat16 1 when the step has items enough to fill the GPU and 16 when it has few.  Warp w takes the key tiles whose number (absolute
 // position / 32) is w modulo VEC_WARPS, keeps its own running maximum, denominator and sums, and warp 0 adds
 // the warps' results in ascending order: which warp visits which tile, and the order of every sum, depend on
 // the query's position only.  A lane owns NV segments of N consecutive value elements among the (value
@@ -346,7 +346,7 @@ static int launch_biased_vec_as(const BiasedArgs& a, cudaStream_t stream) {
         return launch_biased_vec_with<T, NV, 4>(a, stream);
     } else {
         if (static_cast<long long>(a.tokens) * a.heads >= ITEMS_THAT_FILL_THE_GPU) return launch_biased_vec_with<T, NV, 1>(a, stream);
-        return launch_biased_vec_with<T, NV, 8>(a, stream);
+        return launch_biased_vec_with<T, NV, 16>(a, stream);
     }
 }
 
