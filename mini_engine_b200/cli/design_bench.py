@@ -29,7 +29,7 @@ SIZES = {
     "1b": dict(width=2048, ff=6144, heads=16, kv_heads=8, head_dim=128, layers=4, vocab=32768, lin_dim=64, lin_vdim=128, rank=64),
     "8b": dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=4, vocab=32768, lin_dim=128, lin_vdim=128, rank=64),
 }
-TIMED = ("biased_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
+TIMED = ("biased_attention", "mixed_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
          "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding")  # fmt: skip
 
 
@@ -121,7 +121,7 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
     seen_prompt = visible_sum(0, PROMPT, window, keep)
     seen_decode = BATCH * visible_sum(CONTEXT, CONTEXT + 1, window, keep)
     mixing = 2 * h * h if design == "pimezen" else 0  # flops per (query, key) of mixing the heads' weights
-    kind = "biased_attention" if design == "pimezen" else "paged_attention"
+    kind = "mixed_attention" if design == "pimezen" else "paged_attention"
     bound(f"prompt.{kind}", PROMPT * (2 * h * d + 2 * g * d) * 2, seen_prompt * (4 * h * d + mixing))
     bound(f"decode.{kind}", seen_decode * g * 2 * d * 2 + BATCH * 2 * h * d * 2, seen_decode * (4 * h * d + mixing))
     if design == "pimezen":

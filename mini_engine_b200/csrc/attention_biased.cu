@@ -402,6 +402,228 @@ ME_EXPORT int me_biased_attention(const void* q, const void* k_pages, const void
     return type == ME_BF16 ? launch_biased<__nv_bfloat16>(a, stream) : launch_biased<float>(a, stream);
 }
 
+// ------------------------------------------------------------- mixing in two kernels (fewer multiply-adds)
+//
+// The one-pass form above pays kv_heads times the value arithmetic for mixing after the softmax.  The form
+// below keeps the scores instead: kernel 1 writes every (token, head)'s scores of its visible keys (32-bit,
+// compacted: kept tokens first, then the window) and the softmax's maximum and denominator; kernel 2, one block
+// per (token, KV head), turns the scores of ALL heads into normalised weights key by key, mixes them for the
+// heads of its own group and applies the mixed weights to its values.  Per (token, key): heads x dim for the
+// scores, heads x group for the mixing, group x vdim for the values, each once.  Tiles go to warps by tile
+// number and partial results are added in ascending order, as above.
+
+struct ScoreArgs {
+    BiasedArgs a;
+    float* scores;  // [tokens][heads][stride]
+    float* stats;   // [tokens][heads][2] maximum, denominator
+    int stride;     // most keys a query can see
+};
+
+template <typename T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attention_scores_kernel(ScoreArgs s) {
+    constexpr int N = Packed<T>::N;
+    const BiasedArgs& a = s.a;
+    extern __shared__ __align__(16) float score_shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x / a.heads, head = blockIdx.x % a.heads;
+    const int d = a.dim;
+    float* q = score_shared;                         // [dim]
+    float* part_stat = q + ((d + 3) / 4) * 4;        // [WARPS][2]
+    pdl_trigger();
+    const float r1 = a.r1 ? a.r1[head] : 0.0f, r2 = a.r1 ? a.r2[head] : 0.0f;
+    pdl_wait();
+    const int own_kv = head / (a.heads / a.kv_heads);
+    const int position = a.positions[token];
+    const int* table = a.block_table + static_cast<size_t>(a.entry_of_token[token]) * a.table_width;
+    const T* k_pages = static_cast<const T*>(a.k_pages);
+    const T* q_src = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.heads + head) * d;
+    for (int i = threadIdx.x; i < d; i += WARPS * 32) q[i] = to_float(q_src[i]);
+    __syncthreads();
+    const bool packed = d % N == 0 && reinterpret_cast<uintptr_t>(a.k_pages) % 16 == 0;
+    const int lowest = a.window > 0 ? max(position - a.window + 1, 0) : 0;
+    const int kept_end = a.window > 0 ? min(a.keep_first, lowest) : 0;
+    float* row = s.scores + (static_cast<size_t>(token) * a.heads + head) * s.stride;
+    float running_max = -INFINITY, denom = 0.0f;
+    for (int run = 0; run < 2; ++run) {
+        const int from = run == 0 ? 0 : lowest, to = run == 0 ? kept_end - 1 : position;  // inclusive
+        for (int tile = (from / 32) * 32; tile <= to; tile += 32) {
+            if ((tile >> 5) % WARPS != warp) continue;
+            const int key = tile + lane;
+            const bool valid = key >= from && key <= to;
+            int page = -1;
+            if (valid) page = table[key / a.page_size];
+            float score = -INFINITY;
+            if (page >= 0) {
+                const T* k_row = k_pages + ((static_cast<long long>(page) * a.kv_heads + own_kv) * a.page_size + key % a.page_size) * d;
+                float dot = 0.0f;
+                if (packed) {
+#pragma unroll 4
+                    for (int i = 0; i < d; i += N) {
+                        float k[N];
+                        Packed<T>::load(k_row + i, k);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) dot = fmaf(q[i + e], k[e], dot);
+                    }
+                } else {
+                    for (int i = 0; i < d; ++i) dot = fmaf(q[i], to_float(k_row[i]), dot);
+                }
+                score = dot * a.scale;
+                if (a.r1) score -= r1 * logf(1.0f + r2 * static_cast<float>(position - key));
+            }
+            if (valid) row[run == 0 ? key : kept_end + (key - lowest)] = score;
+            const float new_max = fmaxf(running_max, warp_max(score));
+            if (new_max == -INFINITY) continue;
+            const float p = page >= 0 ? expf(score - new_max) : 0.0f;
+            denom = denom * expf(running_max - new_max) + warp_sum(p);
+            running_max = new_max;
+        }
+    }
+    if (lane == 0) {
+        part_stat[warp * 2] = running_max;
+        part_stat[warp * 2 + 1] = denom;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float top = -INFINITY;
+    for (int w = 0; w < WARPS; ++w) top = fmaxf(top, part_stat[w * 2]);
+    float total = 0.0f;
+    for (int w = 0; w < WARPS; ++w)
+        if (part_stat[w * 2] != -INFINITY) total = fmaf(part_stat[w * 2 + 1], expf(part_stat[w * 2] - top), total);
+    float* out = s.stats + (static_cast<size_t>(token) * a.heads + head) * 2;
+    out[0] = top;
+    out[1] = total;
+}
+
+constexpr int MIX_GROUP = 8;    // query heads per KV head, at most
+constexpr int MIX_COLUMNS = 8;  // value elements per lane, at most: vdim <= 256
+
+template <typename T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attention_mix_values_kernel(ScoreArgs s, const float* __restrict__ talk) {
+    const BiasedArgs& a = s.a;
+    extern __shared__ __align__(16) float mix_shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x / a.kv_heads, kv = blockIdx.x % a.kv_heads;
+    const int heads = a.heads, group = heads / a.kv_heads, vd = a.vdim;
+    float* top = mix_shared;                 // [heads]
+    float* inverse = top + heads;            // [heads] 1 / denominator
+    float* mixing = inverse + heads;         // [group][heads] rows of the mixing matrix for this group's heads
+    float* partial = mixing + group * heads; // [WARPS][group][vd]
+    pdl_trigger();
+    for (int i = threadIdx.x; i < group * heads; i += WARPS * 32) mixing[i] = talk[(kv * group + i / heads) * heads + i % heads];
+    pdl_wait();
+    for (int g = threadIdx.x; g < heads; g += WARPS * 32) {
+        const float* st = s.stats + (static_cast<size_t>(token) * heads + g) * 2;
+        top[g] = st[0];
+        inverse[g] = 1.0f / st[1];
+    }
+    __syncthreads();
+    const int position = a.positions[token];
+    const int* table = a.block_table + static_cast<size_t>(a.entry_of_token[token]) * a.table_width;
+    const T* v_pages = static_cast<const T*>(a.v_pages);
+    const int lowest = a.window > 0 ? max(position - a.window + 1, 0) : 0;
+    const int kept_end = a.window > 0 ? min(a.keep_first, lowest) : 0;
+    const float* rows = s.scores + static_cast<size_t>(token) * heads * s.stride;
+    float acc[MIX_GROUP][MIX_COLUMNS];
+#pragma unroll
+    for (int h = 0; h < MIX_GROUP; ++h)
+#pragma unroll
+        for (int i = 0; i < MIX_COLUMNS; ++i) acc[h][i] = 0.0f;
+    for (int run = 0; run < 2; ++run) {
+        const int from = run == 0 ? 0 : lowest, to = run == 0 ? kept_end - 1 : position;  // inclusive
+        for (int tile = (from / 32) * 32; tile <= to; tile += 32) {
+            if ((tile >> 5) % WARPS != warp) continue;
+            const int key = tile + lane;
+            const bool valid = key >= from && key <= to;
+            long long value_row = -1;  // element offset of this key's values in this KV head
+            float mixed[MIX_GROUP];
+#pragma unroll
+            for (int h = 0; h < MIX_GROUP; ++h) mixed[h] = 0.0f;
+            if (valid) {
+                const int page = table[key / a.page_size];
+                if (page >= 0) {
+                    value_row = ((static_cast<long long>(page) * a.kv_heads + kv) * a.page_size + key % a.page_size) * vd;
+                    const int index = run == 0 ? key : kept_end + (key - lowest);
+                    for (int g = 0; g < heads; ++g) {  // ascending g: the order of the mixed sum
+                        const float w = expf(rows[static_cast<size_t>(g) * s.stride + index] - top[g]) * inverse[g];
+#pragma unroll
+                        for (int h = 0; h < MIX_GROUP; ++h)
+                            if (h < group) mixed[h] = fmaf(mixing[h * heads + g], w, mixed[h]);
+                    }
+                }
+            }
+            for (int j = 0; j < 32; ++j) {
+                const long long rj = __shfl_sync(0xffffffffu, value_row, j);
+                float wj[MIX_GROUP];
+#pragma unroll
+                for (int h = 0; h < MIX_GROUP; ++h) wj[h] = __shfl_sync(0xffffffffu, mixed[h], j);
+                if (rj < 0) continue;  // uniform across the warp
+                const T* v_row = v_pages + rj;
+#pragma unroll
+                for (int i = 0; i < MIX_COLUMNS; ++i) {
+                    const int e = lane + 32 * i;
+                    if (e < vd) {
+                        const float v = to_float(v_row[e]);
+#pragma unroll
+                        for (int h = 0; h < MIX_GROUP; ++h) acc[h][i] = fmaf(wj[h], v, acc[h][i]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < MIX_GROUP; ++h)
+#pragma unroll
+        for (int i = 0; i < MIX_COLUMNS; ++i) {
+            const int e = lane + 32 * i;
+            if (h < group && e < vd) partial[(warp * group + h) * vd + e] = acc[h][i];
+        }
+    __syncthreads();
+    T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * heads + kv * group) * vd;
+    for (int i = threadIdx.x; i < group * vd; i += WARPS * 32) {
+        float sum = 0.0f;
+        for (int w = 0; w < WARPS; ++w) sum += partial[w * group * vd + i];
+        out[i] = from_float<T>(sum);
+    }
+}
+
+template <typename T, int WARPS>
+static int launch_two_kernels(const ScoreArgs& s, const float* talk, cudaStream_t stream) {
+    static SharedMemoryOptIn opt_in;
+    const BiasedArgs& a = s.a;
+    const int group = a.heads / a.kv_heads;
+    const size_t smem1 = (static_cast<size_t>((a.dim + 3) / 4) * 4 + WARPS * 2) * sizeof(float);
+    const size_t smem2 = (static_cast<size_t>(2) * a.heads + static_cast<size_t>(group) * a.heads + static_cast<size_t>(WARPS) * group * a.vdim) * sizeof(float);
+    if (smem1 > 48 * 1024 || smem2 > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    if (smem2 > 48 * 1024) {
+        const int code = opt_in(attention_mix_values_kernel<T, WARPS>, static_cast<int>(smem2));
+        if (code) return code;
+    }
+    int code = launch_kernel_in_order(attention_scores_kernel<T, WARPS>, a.tokens * a.heads, WARPS * 32, smem1, stream, s);
+    if (code) return code;
+    return launch_kernel_in_order(attention_mix_values_kernel<T, WARPS>, a.tokens * a.kv_heads, WARPS * 32, smem2, stream, s, talk);
+}
+
+// Mixed attention in two kernels.  `scores` holds tokens * heads * stride floats, `stats` tokens * heads * 2;
+// `stride` is the most keys a query of this step can see.  out: [tokens][heads][vdim] of the pages' type.
+ME_EXPORT int me_mixed_attention(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                 const int* entry_of_token, const int* positions, const float* r1, const float* r2,
+                                 const float* talk, float* scores, float* stats, int stride, void* out, int type,
+                                 float scale, int tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                                 int table_width, int window, int keep_first, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads % kv_heads || heads / kv_heads > MIX_GROUP || vdim > 32 * MIX_COLUMNS || dim < 1 || vdim < 1) return ME_ERR_UNSUPPORTED;
+    if ((r1 == nullptr) != (r2 == nullptr) || window < 0 || keep_first < 0 || talk == nullptr || stride < 1) return ME_ERR_ARGUMENT;
+    if (static_cast<long long>(tokens) * heads > 0x7fffffffll) return ME_ERR_UNSUPPORTED;
+    ScoreArgs s{{q, k_pages, v_pages, block_table, entry_of_token, positions, r1, r2, out, scale, tokens, heads,
+                 kv_heads, dim, vdim, page_size, table_width, window, keep_first, 0},
+                scores, stats, stride};
+    // float32: four warps always (the same bits for a token in a prompt and decoded alone); bfloat16: two
+    // warps when the step has blocks enough to fill the GPU, sixteen when it has few.
+    if (type != ME_BF16) return launch_two_kernels<float, 4>(s, talk, stream);
+    if (static_cast<long long>(tokens) * kv_heads >= 1024) return launch_two_kernels<__nv_bfloat16, 2>(s, talk, stream);
+    return launch_two_kernels<__nv_bfloat16, 16>(s, talk, stream);
+}
+
 // out[t][h][e] = sum_g talk[h][g] * spread[t][g][kv(h)][e], ascending g.
 template <typename T>
 __global__ void mix_heads_kernel(const float* __restrict__ spread, const float* __restrict__ talk, T* __restrict__ out,

@@ -458,6 +458,45 @@ def biased_attention(
         _check(code, "mix_heads")
 
 
+MIXED_ATTENTION_MAX_GROUP, MIXED_ATTENTION_MAX_VALUE_DIM = 8, 256
+
+
+def mixed_attention(
+    *, q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads: int, kv_heads: int, head_dim: int,
+    value_dim: int, scale: float, window: int, keep_first: int, r1: torch.Tensor | None, r2: torch.Tensor | None,
+    talk: torch.Tensor, scores: torch.Tensor, stats: torch.Tensor, stride: int,
+) -> None:  # fmt: skip
+    """The attention of :func:`biased_attention` with mixed heads, in two kernels that keep the scores
+    (``scores``: float32 scratch of ``T * heads * stride`` values, ``stride`` the most keys a query can see;
+    ``stats``: ``T * heads * 2``) and apply every value once.  Groups of up to 8 query heads per KV head,
+    value heads up to 256 wide."""
+    _need(q, None, "q"), _need(out, q.dtype, "out"), _need(k_pages, q.dtype, "k_pages"), _need(v_pages, q.dtype, "v_pages")
+    _need(block_table, torch.int32, "block_table"), _need(entry_of_token, torch.int32, "entry_of_token")
+    _need(positions, torch.int32, "positions"), _need(talk, torch.float32, "talk")
+    _need(scores, torch.float32, "scores"), _need(stats, torch.float32, "stats")
+    tokens = q.shape[0]
+    for name, vector in (("r1", r1), ("r2", r2)):
+        if vector is not None:
+            _need(vector, torch.float32, name)
+            if vector.shape != (heads,):
+                raise KernelError(f"{name} must have one value per head")
+    if k_pages.shape[1:] != (kv_heads, k_pages.shape[2], head_dim) or v_pages.shape[1:] != (kv_heads, k_pages.shape[2], value_dim):
+        raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit the head sizes")
+    if talk.shape != (heads, heads) or scores.numel() < tokens * heads * stride or stats.numel() < tokens * heads * 2:
+        raise KernelError("talk must be [heads, heads]; scores and stats must hold the step's (token, head) pairs")
+    fn = _fn(
+        "attention_biased",
+        "me_mixed_attention",
+        [c_void_p] * 11 + [c_int, c_void_p, c_int, c_float] + [c_int] * 9 + [c_void_p],
+    )
+    code = fn(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _ptr(entry_of_token), _ptr(positions), _ptr(r1), _ptr(r2),
+        _ptr(talk), _ptr(scores), _ptr(stats), int(stride), _ptr(out), _type_code(q.dtype), float(scale), tokens, heads,
+        kv_heads, head_dim, value_dim, k_pages.shape[2], block_table.shape[1], int(window), int(keep_first), _stream(),
+    )  # fmt: skip
+    _check(code, "mixed_attention")
+
+
 def branch_sum(branches: list[tuple[torch.Tensor, float]], out: torch.Tensor) -> None:
     """``out [T, width] = sum_b factor_b * sum_s partial_b[s]`` for up to four ``[S, T, width]`` float32
     partial-sum arrays."""

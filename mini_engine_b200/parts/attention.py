@@ -83,6 +83,13 @@ class GroupedQueryAttention(Mixer):
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden_size, num_heads, kv_heads, head_dim
         self.qk_norm_eps = qk_norm_eps
         self.window = window
+        # Mixed heads under a window run as two kernels that keep the scores of the (bounded) visible keys, when
+        # the sizes fit them and the scratch of a 2,048-token step stays under 1 GiB; else in one pass.
+        self.two_kernel_mixing = bool(
+            self.talking_heads and window
+            and num_heads // kv_heads <= ops.MIXED_ATTENTION_MAX_GROUP and self.value_dim <= ops.MIXED_ATTENTION_MAX_VALUE_DIM
+            and 2048 * num_heads * (window + self.keep_first) * 4 <= 1 << 30
+        )  # fmt: skip
         self.scale = float(scale) if scale is not None else head_dim**-0.5
         self.reads_shared_cache = reads_shared_cache
         self.qkv_bias = qkv_bias  # the reference's projections have none (src/mini_engine/model.py:97-100)
@@ -196,6 +203,19 @@ class GroupedQueryAttention(Mixer):
             ops.kv_store(k_new, v_new, slots, cache.k, cache.v, kv_in, d, ctx.page_size)
         if self.extended:
             out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
+            if self.two_kernel_mixing:
+                # Scores of every visible key are kept between two kernels; a window bounds them whatever the context.
+                stride = self.window + self.keep_first
+                scores = ctx.buffer("attn.scores", (tokens, self.heads * stride), torch.float32)
+                stats = ctx.buffer("attn.stats", (tokens, self.heads * 2), torch.float32)
+                ops.mixed_attention(
+                    q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group],
+                    entry_of_token=ctx.entry_of_token, positions=ctx.positions, out=out, heads=self.heads,
+                    kv_heads=self.kv_heads, head_dim=d, value_dim=self.value_dim, scale=self.scale, window=self.window,
+                    keep_first=self.keep_first, r1=self.r1, r2=self.r2, talk=self.talk, scores=scores, stats=stats,
+                    stride=stride,
+                )  # fmt: skip
+                return self.out.forward(out, ctx, "attn.o")
             spread = None
             if self.talk is not None:
                 spread = ctx.buffer("attn.spread", (tokens, self.heads * self.kv_heads * self.value_dim), torch.float32)

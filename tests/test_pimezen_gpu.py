@@ -263,6 +263,21 @@ def run_attention(q, k, v, r1, r2, talk, scale, window, keep_first, positions, d
         r2=cuda(r2, torch.float32), talk=cuda(talk, torch.float32), spread=spread,
     )  # fmt: skip
     torch.cuda.synchronize()
+    if talk is not None and window and H // G <= 8 and V <= 256:  # the same through the two-kernel form
+        stride = window + keep_first
+        again = torch.empty_like(out)
+        ops.mixed_attention(
+            q=cuda(q[positions], dtype), k_pages=cuda(k_pages, dtype), v_pages=cuda(v_pages, dtype),
+            block_table=cuda(table.view(1, -1)), entry_of_token=torch.zeros(n, dtype=torch.int32, device="cuda"),
+            positions=torch.tensor(positions, dtype=torch.int32, device="cuda"), out=again, heads=H, kv_heads=G,
+            head_dim=D, value_dim=V, scale=scale, window=window, keep_first=keep_first, r1=cuda(r1, torch.float32),
+            r2=cuda(r2, torch.float32), talk=cuda(talk, torch.float32),
+            scores=torch.full((n * H * stride,), float("nan"), device="cuda"), stats=torch.empty(n * H * 2, device="cuda"),
+            stride=stride,
+        )  # fmt: skip
+        torch.cuda.synchronize()
+        tolerance = 3e-5 if dtype == torch.float32 else 3e-2
+        assert torch.allclose(again.float(), out.float(), atol=tolerance * max(1.0, float(out.float().abs().max())), rtol=tolerance)
     return out.float().cpu().view(n, H, V)
 
 
@@ -318,6 +333,11 @@ def test_a_key_that_stands_out_at_an_edge(window, keep_first, offset):
     for positions in (list(range(T)), [position]):  # in a prompt of all tokens, and decoded alone
         got = run_attention(q, k, v, r1, r2, None, 1.0, window, keep_first, positions, torch.float32)
         assert torch.allclose(got, want[positions], atol=3e-5, rtol=1e-4)
+    talk = torch.tensor([[0.25, 0.75], [-0.5, 1.5]])  # mixed heads: both forms of the kernels at the same edges
+    mixed = plain_attention(q, k, v, r1, r2, talk, 1.0, window, keep_first)
+    for positions in (list(range(T)), [position]):
+        got = run_attention(q, k, v, r1, r2, talk, 1.0, window, keep_first, positions, torch.float32)
+        assert torch.allclose(got, mixed[positions], atol=3e-5, rtol=1e-4)
     got = run_attention(q, k, v, r1, r2, None, 1.0, window, keep_first, [position], torch.bfloat16, page_size=8)
     assert torch.allclose(got, want[[position]], atol=3e-2, rtol=3e-2)
 
