@@ -159,7 +159,6 @@ def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dic
             function()
             end.record()
             torch.cuda.synchronize()
-            print(f"[design_bench]   iteration {i}: {start.elapsed_time(end):.2f} ms", file=sys.stderr, flush=True)
             if i >= warm:
                 times.append(start.elapsed_time(end))
         return statistics.median(times)

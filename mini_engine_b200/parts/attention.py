@@ -84,11 +84,10 @@ class GroupedQueryAttention(Mixer):
         self.qk_norm_eps = qk_norm_eps
         self.window = window
         # Mixed heads under a window run as two kernels that keep the scores of the (bounded) visible keys, when
-        # the sizes fit them and the scratch of a 2,048-token step stays under 1 GiB; else in one pass.
+        # the sizes fit them (and, decided per engine in `forward`, the scratch stays under 2 GiB); else in one pass.
         self.two_kernel_mixing = bool(
             self.talking_heads and window
             and num_heads // kv_heads <= ops.MIXED_ATTENTION_MAX_GROUP and self.value_dim <= ops.MIXED_ATTENTION_MAX_VALUE_DIM
-            and 2048 * num_heads * (window + self.keep_first) * 4 <= 1 << 30
         )  # fmt: skip
         self.scale = float(scale) if scale is not None else head_dim**-0.5
         self.reads_shared_cache = reads_shared_cache
@@ -203,9 +202,11 @@ class GroupedQueryAttention(Mixer):
             ops.kv_store(k_new, v_new, slots, cache.k, cache.v, kv_in, d, ctx.page_size)
         if self.extended:
             out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
-            if self.two_kernel_mixing:
-                # Scores of every visible key are kept between two kernels; a window bounds them whatever the context.
-                stride = self.window + self.keep_first
+            # Scores of every visible key are kept between two kernels; a window bounds them whatever the context.
+            # The scratch is sized for the engine's token capacity, so the choice never depends on the batch.
+            stride = (self.window or 0) + self.keep_first
+            capacity = max(tokens, ctx.workspace.max_tokens)
+            if self.two_kernel_mixing and capacity * self.heads * stride * 4 <= 2 << 30:
                 scores = ctx.buffer("attn.scores", (tokens, self.heads * stride), torch.float32)
                 stats = ctx.buffer("attn.stats", (tokens, self.heads * 2), torch.float32)
                 ops.mixed_attention(
