@@ -32,8 +32,8 @@ from mini_engine_b200.weights.loader import WeightSpec
 @register("mixer", "gated_linear_attention")
 class GatedLinearAttention(Mixer):
     capturable = True
-    # Prompt steps of a model with this mixer at widths of 4,096 stalled on a B200 while their kernels were
-    # launched as programmatic dependents (seven 2,048-token steps in a row, every time) and ran through in
+    # Prompt steps of a model with this mixer at widths of 4,096 stalled on a B200 when every kernel of the step
+    # was launched as a programmatic dependent (after 5 to 12 steps of 2,048 tokens in a row) and ran through in
     # plain stream order; which kernels meet badly is not known, so such a model's steps run in order.
     programmatic_launch = False
 
