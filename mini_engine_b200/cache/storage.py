@@ -12,7 +12,7 @@ share a group, hence a page pool and block tables.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 
@@ -26,8 +26,9 @@ class CacheLayout:
     group_specs: list[PagedCacheSpec]
     views: list[LayerCache]  # one per execution entry
     arrays: list[torch.Tensor]  # per group [entries, 2, pages + 1, kv_heads, block_size, head_dim]; keys and values apart when their widths differ
-    slot_groups: list[SlotGroupSpec]  # one per execution entry whose mixer keeps per-request state
+    slot_groups: list[SlotGroupSpec]  # one per execution entry whose mixer keeps per-request state (and the embedding's)
     bytes_per_token: int
+    embedding_state: torch.Tensor | None = None  # [max_num_seqs + 1, *shape] when the embedding part keeps a state
 
     @property
     def has_state(self) -> bool:
@@ -39,24 +40,37 @@ class CacheLayout:
         return [g.num_blocks for g in self.groups]
 
 
+def _widest(a: int | None, b: int | None) -> int | None:
+    return None if a is None or b is None else max(a, b)
+
+
 def plan_groups(needs) -> tuple[list[PagedCacheSpec], list[int | None]]:
     """Group the execution entries by equal per-token need.  Returns the distinct needs and,
-    per entry, its group index (``None`` for an entry without per-token cache)."""
+    per entry, its group index (``None`` for an entry without per-token cache).  An entry that
+    reads another entry's cache may look back over a window of its own; the owner then keeps its
+    pages for the widest window of all its readers (and for all time if one of them has none)."""
+    kept: dict[int, PagedCacheSpec] = {}  # owning entry -> what it has to keep
+    for entry, (paged, _state, cache_of) in enumerate(needs):
+        if paged is None:
+            continue
+        if cache_of is None:
+            kept[entry] = paged
+            continue
+        owner = needs[cache_of][0]
+        if owner is None or replace(owner, window=paged.window) != paged:
+            raise ValueError(f"an entry reads a cache of {owner} but its mixer expects {paged}")
+        kept[cache_of] = replace(kept[cache_of], window=_widest(kept[cache_of].window, paged.window))
     specs: list[PagedCacheSpec] = []
     group_of: list[int | None] = []
-    for paged, _state, cache_of in needs:
+    for entry, (paged, _state, cache_of) in enumerate(needs):
         if paged is None:
             group_of.append(None)
-            continue
-        if cache_of is not None:
-            owner = needs[cache_of][0]
-            if owner != paged:
-                raise ValueError(f"an entry reads a cache of {owner} but its mixer expects {paged}")
+        elif cache_of is not None:
             group_of.append(group_of[cache_of])
-            continue
-        if paged not in specs:
-            specs.append(paged)
-        group_of.append(specs.index(paged))
+        else:
+            if kept[entry] not in specs:
+                specs.append(kept[entry])
+            group_of.append(specs.index(kept[entry]))
     return specs, group_of
 
 
@@ -124,6 +138,7 @@ def allocate_cache(
     dtype: torch.dtype,
     device: str | torch.device = "cuda",
     max_step_tokens: int | None = None,
+    embedding_state: StateSpec | None = None,
 ) -> CacheLayout:
     """``max_step_tokens`` (the token budget of a step) bounds what a group with a window can
     hold; without it such a group is sized like one that keeps every key."""
@@ -164,4 +179,8 @@ def allocate_cache(
             view.state = torch.zeros((max_num_seqs + 1, *state.shape), dtype=state.dtype, device=device)
         views.append(view)
     per_token = sum(len(e) * s.kv_heads * (s.head_dim + s.v_dim) * element for s, e in zip(specs, owners))
-    return CacheLayout(group_names(specs, pages), specs, views, arrays, slot_groups, per_token)
+    first_state = None
+    if embedding_state is not None:
+        slot_groups.append(SlotGroupSpec(f"embedding:{'x'.join(map(str, embedding_state.shape))}"))
+        first_state = torch.zeros((max_num_seqs + 1, *embedding_state.shape), dtype=embedding_state.dtype, device=device)
+    return CacheLayout(group_names(specs, pages), specs, views, arrays, slot_groups, per_token, first_state)

@@ -5,7 +5,9 @@
 // Formula (YuvGev00/mini-engine, src/mini_engine/attention.py:84-86,160-175 and the online
 // softmax of src/mini_engine/triton_attention.py:56-82): query head h reads KV head h / group;
 // s = (q . k) * scale; the query at position p sees keys at positions <= p (and > p - window
-// when a window is given); out = softmax(s) V.
+// when a window is given); out = softmax(s) V.  Options: value heads of their own width (`value_dim`); a
+// softmax with one more, silent participant of score zero that has no value (`sink`: p_j = exp(s_j) /
+// (1 + sum exp(s))); and a multiplier per (token, head) on the output (`gate`, float32 [tokens][heads]).
 //
 // Keys are visited in tiles of 32 whose boundaries are multiples of 32 in *absolute position*
 // and are combined in ascending order, so the arithmetic of a query depends only on its own
@@ -20,9 +22,11 @@ struct AttnArgs {
     const int* block_table;  // [entries][table_width]
     const int* entry_of_token;
     const int* positions;
-    void* out;  // [tokens][heads][head_dim]
+    void* out;  // [tokens][heads][value_dim]
     float scale;
     int tokens, heads, kv_heads, head_dim, page_size, table_width, window;
+    int value_dim, sink;
+    const float* gate;  // [tokens][heads] or null
 };
 
 constexpr int ATTN_WARPS = 4;
@@ -35,7 +39,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
     const long long item = static_cast<long long>(blockIdx.x) * ATTN_WARPS + warp;
     if (item >= static_cast<long long>(a.tokens) * a.heads) return;
     const int token = static_cast<int>(item / a.heads), head = static_cast<int>(item % a.heads);
-    const int d = a.head_dim;
+    const int d = a.head_dim, dv = a.value_dim;
     pdl_trigger();
     pdl_wait();
     const int kv_head = head / (a.heads / a.kv_heads);
@@ -58,15 +62,15 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
     for (int tile = (lowest / 32) * 32; tile <= position; tile += 32) {
         const int key = tile + lane;
         const bool valid = key >= lowest && key <= position;
-        long long base = -1;  // element offset of this lane's key row, -1 when masked
+        long long base = -1;  // row of this lane's key in the pages, -1 when masked
         if (valid) {
             const int page = table[key / a.page_size];
             if (page >= 0)
-                base = ((static_cast<long long>(page) * a.kv_heads + kv_head) * a.page_size + key % a.page_size) * d;
+                base = (static_cast<long long>(page) * a.kv_heads + kv_head) * a.page_size + key % a.page_size;
         }
         float score = -INFINITY;
         if (base >= 0) {
-            const T* k_row = k_pages + base;
+            const T* k_row = k_pages + base * d;
             float dot = 0.0f;
             for (int i = 0; i < d; ++i) dot = fmaf(q[i], to_float(k_row[i]), dot);
             score = dot * a.scale;
@@ -83,20 +87,22 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long bj = __shfl_sync(0xffffffffu, base, j);
             if (bj < 0) continue;  // uniform across the warp
-            const T* v_row = v_pages + bj;
+            const T* v_row = v_pages + bj * dv;
 #pragma unroll
             for (int i = 0; i < MAX_DIM_PER_LANE; ++i) {
                 const int e = lane + 32 * i;
-                if (e < d) acc[i] = fmaf(pj, to_float(v_row[e]), acc[i]);
+                if (e < dv) acc[i] = fmaf(pj, to_float(v_row[e]), acc[i]);
             }
         }
     }
-    T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.heads + head) * d;
-    const float inv = 1.0f / denom;
+    T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.heads + head) * dv;
+    if (a.sink) denom += expf(-running_max);  // the silent participant: exp(0 - max)
+    float inv = 1.0f / denom;
+    if (a.gate) inv *= a.gate[static_cast<size_t>(token) * a.heads + head];
 #pragma unroll
     for (int i = 0; i < MAX_DIM_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        if (e < d) out[e] = from_float<T>(acc[i] * inv);
+        if (e < dv) out[e] = from_float<T>(acc[i] * inv);
     }
 }
 
@@ -104,11 +110,13 @@ ME_EXPORT int me_paged_attention_generic(const void* q, const void* k_pages, con
                                          const int* block_table, const int* entry_of_token,
                                          const int* positions, void* out, int type, float scale, int tokens,
                                          int heads, int kv_heads, int head_dim, int page_size, int table_width,
-                                         int window, cudaStream_t stream) {
+                                         int window, int value_dim, int sink, const float* gate,
+                                         cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (head_dim > 32 * MAX_DIM_PER_LANE || heads % kv_heads) return ME_ERR_UNSUPPORTED;
+    if (head_dim > 32 * MAX_DIM_PER_LANE || value_dim < 1 || value_dim > 32 * MAX_DIM_PER_LANE || heads % kv_heads)
+        return ME_ERR_UNSUPPORTED;
     AttnArgs a{q, k_pages, v_pages, block_table, entry_of_token, positions, out, scale,
-               tokens, heads, kv_heads, head_dim, page_size, table_width, window};
+               tokens, heads, kv_heads, head_dim, page_size, table_width, window, value_dim, sink, gate};
     const long long items = static_cast<long long>(tokens) * heads;
     const int blocks = static_cast<int>((items + ATTN_WARPS - 1) / ATTN_WARPS);
     const size_t smem = static_cast<size_t>(ATTN_WARPS) * head_dim * sizeof(float);

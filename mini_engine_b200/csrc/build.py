@@ -34,6 +34,8 @@ LIBRARIES = {
     "attention_generic": "attention_generic.cu",
     "attention_biased": "attention_biased.cu",
     "linear_attention": "linear_attention.cu",
+    "recurrent": "recurrent.cu",
+    "routing": "routing.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_tcgen05": "attention_tcgen05.cu",

@@ -122,7 +122,8 @@ template <typename OutT, bool VEC, int LANES, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
                    const float* __restrict__ weight, float eps, OutT* __restrict__ out,
-                   const int* __restrict__ rows, int hidden, const float* __restrict__ pending_scale) {
+                   const int* __restrict__ rows, int hidden, const float* __restrict__ pending_scale,
+                   float x_scale, int keep_normed) {
     constexpr int PLAYED = LANES / THREADS;  // lanes per thread
     extern __shared__ float row_cache[];  // [hidden]
     __shared__ float warp_partial[LANES / 32];
@@ -136,7 +137,9 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     pdl_wait();
     float* x_row = x + static_cast<size_t>(src) * hidden;
     const float* pending_row = pending + static_cast<size_t>(src) * hidden;
-    const bool write_back = !rows && splits > 0;
+    // keep_normed: the stream itself becomes the normalised row (a layer whose norm follows the sum).
+    const bool write_back = !rows && splits > 0 && !keep_normed;
+    const bool write_normed = !rows && keep_normed;
     float sum_sq[PLAYED];
 #pragma unroll
     for (int k = 0; k < PLAYED; ++k) sum_sq[k] = 0.0f;
@@ -147,6 +150,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
                 const int i = base + (k * THREADS + threadIdx.x) * 4;
                 if (i >= hidden) continue;
                 float4 v = *reinterpret_cast<const float4*>(x_row + i);
+                v.x *= x_scale; v.y *= x_scale; v.z *= x_scale; v.w *= x_scale;  // 1 in a pre-norm layer: exact
                 float4 part[MAX_UNROLLED_SPLITS];
 #pragma unroll
                 for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
@@ -178,7 +182,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
             for (int k = 0; k < PLAYED; ++k) {
                 const int i = base + k * THREADS + threadIdx.x;
                 if (i >= hidden) continue;
-                float v = x_row[i];
+                float v = x_row[i] * x_scale;
                 if (pending_scale != nullptr && splits > 0) {
                     float sum = pending_row[i];
                     for (int s = 1; s < splits; ++s) sum += pending_row[s * split_stride + i];
@@ -207,23 +211,28 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
         for (int i = threadIdx.x * 4; i < hidden; i += THREADS * 4) {
             const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
             const float4 w = i == threadIdx.x * 4 ? first_weight : *reinterpret_cast<const float4*>(weight + i);
-            store4(out_ptr + i, make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv)));
+            const float4 y = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
+            store4(out_ptr + i, y);
+            if (write_normed) *reinterpret_cast<float4*>(x_row + i) = y;
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += THREADS)
-            out_ptr[i] = from_float<OutT>(weight[i] * (row_cache[i] * inv));
+        for (int i = threadIdx.x; i < hidden; i += THREADS) {
+            const float y = weight[i] * (row_cache[i] * inv);
+            out_ptr[i] = from_float<OutT>(y);
+            if (write_normed) x_row[i] = y;
+        }
     }
 }
 
 template <typename OutT, bool VEC, int LANES, int THREADS>
 static int launch_add_rmsnorm_threads(float* x, const float* pending, int splits, size_t split_stride,
                                       const float* weight, float eps, OutT* out, const int* rows, int count, int hidden,
-                                      cudaStream_t stream, const float* pending_scale) {
+                                      cudaStream_t stream, const float* pending_scale, float x_scale, int keep_normed) {
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
     auto kernel = add_rmsnorm_kernel<OutT, VEC, LANES, THREADS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_kernel(kernel, count, THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
-                         rows, hidden, pending_scale);
+                         rows, hidden, pending_scale, x_scale, keep_normed);
 }
 
 // Few rows: one lane per thread.  Many rows: 256 threads per row, more rows per SM.  The lanes
@@ -233,28 +242,29 @@ constexpr int NORM_MANY_ROWS = 256;
 template <typename OutT, bool VEC, int LANES>
 static int launch_add_rmsnorm_lanes(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
                                     float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream,
-                                    const float* pending_scale) {
+                                    const float* pending_scale, float x_scale, int keep_normed) {
     if (count >= NORM_MANY_ROWS)
-        return launch_add_rmsnorm_threads<OutT, VEC, LANES, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
-    return launch_add_rmsnorm_threads<OutT, VEC, LANES, LANES>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
+        return launch_add_rmsnorm_threads<OutT, VEC, LANES, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
+    return launch_add_rmsnorm_threads<OutT, VEC, LANES, LANES>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
 }
 
 template <typename OutT, bool VEC>
 static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
                               float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream,
-                                    const float* pending_scale) {
+                                    const float* pending_scale, float x_scale, int keep_normed) {
     if (VEC && hidden > 2048)
-        return launch_add_rmsnorm_lanes<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
     if (VEC && hidden > 1024)
-        return launch_add_rmsnorm_lanes<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
-    return launch_add_rmsnorm_lanes<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
+    return launch_add_rmsnorm_lanes<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long long split_stride,
                              const float* weight, float eps, void* out, int out_type, const int* rows,
-                             int count, int hidden, const float* pending_scale, cudaStream_t stream) {
+                             int count, int hidden, const float* pending_scale, float x_scale, int keep_normed,
+                             cudaStream_t stream) {
     if (count <= 0) return 0;
     if (static_cast<size_t>(hidden) * sizeof(float) > 200 * 1024) return ME_ERR_UNSUPPORTED;
     // Which path runs depends on the width and on the alignment of the engine's persistent
@@ -264,12 +274,12 @@ ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long lo
     const size_t stride = static_cast<size_t>(split_stride);
     if (out_type == ME_BF16) {
         auto* o = static_cast<__nv_bfloat16*>(out);
-        return vec ? launch_add_rmsnorm<__nv_bfloat16, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale)
-                   : launch_add_rmsnorm<__nv_bfloat16, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale);
+        return vec ? launch_add_rmsnorm<__nv_bfloat16, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale, x_scale, keep_normed)
+                   : launch_add_rmsnorm<__nv_bfloat16, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
     }
     auto* o = static_cast<float*>(out);
-    return vec ? launch_add_rmsnorm<float, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale)
-               : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale);
+    return vec ? launch_add_rmsnorm<float, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale, x_scale, keep_normed)
+               : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
 }
 
 // --------------------------------------------------------------------------------- SwiGLU
@@ -279,7 +289,8 @@ ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long lo
 // slope 1, no limit and offset 0 are silu(gate) * up.
 template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
-                              OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset) {
+                              OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset,
+                              const float* __restrict__ group_weight, int group_size, int groups) {
     const size_t total = static_cast<size_t>(tokens) * inter;
     pdl_trigger();
     pdl_wait();
@@ -298,21 +309,28 @@ __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, siz
             up = fminf(fmaxf(up, -limit), limit);
         }
         const float activated = gate / (1.0f + expf(-slope * gate));
-        out[idx] = from_float<OutT>(activated * (up + offset));
+        float value = activated * (up + offset);
+        // routed units: feature i belongs to unit i / group_size, whose weight for this token may be zero
+        if (group_weight != nullptr) value *= group_weight[t * groups + i / group_size];
+        out[idx] = from_float<OutT>(value);
     }
 }
 
 ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride, void* out, int out_type,
-                        int tokens, int inter, float slope, float limit, float offset, cudaStream_t stream) {
+                        int tokens, int inter, float slope, float limit, float offset, const float* group_weight,
+                        int group_size, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (group_weight != nullptr && (group_size < 1 || inter % group_size)) return ME_ERR_ARGUMENT;
+    const int groups = group_weight != nullptr ? inter / group_size : 0;
     const size_t total = static_cast<size_t>(tokens) * inter;
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
     if (out_type == ME_BF16)
         return launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, partial, splits,
-                             (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset);
+                             (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset,
+                             group_weight, group_size, groups);
     return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
-                         static_cast<float*>(out), tokens, inter, slope, limit, offset);
+                         static_cast<float*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups);
 }
 
 // ------------------------------------------------- per-head norm + rotary + cache write
@@ -638,4 +656,226 @@ ME_EXPORT int me_branch_sum(const float* const* partials, const int* splits, con
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
     return launch_kernel(branch_sum_kernel, blocks, threads, 0, stream, a, out, total);
+}
+
+// --------------------------------------------------- embedding with a second, pair-hashed table
+
+// out[t] = table[id_t] * multiplier + pair_table[row_t], float32, one block per token.  row_t is
+// (previous id * mul_prev + id_t * mul_cur) mod buckets, and `buckets` (the table's last row) for the
+// first token of a sequence.  The previous id of an entry's first token is the request's state
+// (last_token[slot]; nothing when the entry starts its sequence); the block of an entry's first token
+// also leaves the entry's last id there for the next step.  `rounded` (optional) receives the same row
+// in the compute dtype for a first layer that reads the stream itself.
+struct PairEmbeddingArgs {
+    const void* table;
+    const void* pair_table;
+    const int* ids;
+    const int* entry_of_token;
+    const int* cu_tokens;
+    const int* state_slots;
+    const int* fresh;
+    int* last_token;  // [slots + 1]
+    float* out;
+    void* rounded;
+    int hidden, vocab, buckets;
+    long long mul_prev, mul_cur;
+    float multiplier;
+};
+
+template <typename T, typename RoundT>
+__global__ void pair_embedding_kernel(PairEmbeddingArgs a) {
+    const int token = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    const int id = a.ids[token];
+    const int entry = a.entry_of_token[token];
+    const int first = a.cu_tokens[entry];
+    int previous = -1;
+    if (token != first) previous = a.ids[token - 1];
+    else if (!a.fresh[entry]) previous = a.last_token[a.state_slots[entry]];
+    __syncthreads();  // every thread has read the state before one of them replaces it
+    if (token == first && threadIdx.x == 0) a.last_token[a.state_slots[entry]] = a.ids[a.cu_tokens[entry + 1] - 1];
+    float* row_out = a.out + static_cast<size_t>(token) * a.hidden;
+    RoundT* row_rounded = a.rounded ? static_cast<RoundT*>(a.rounded) + static_cast<size_t>(token) * a.hidden : nullptr;
+    if (id < 0 || id >= a.vocab) {  // the host validates ids; never read outside the table
+        for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
+            row_out[i] = 0.0f;
+            if (row_rounded) row_rounded[i] = from_float<RoundT>(0.0f);
+        }
+        return;
+    }
+    long long pair = a.buckets;
+    if (previous >= 0) pair = (previous * a.mul_prev + id * a.mul_cur) % a.buckets;
+    const T* row = static_cast<const T*>(a.table) + static_cast<size_t>(id) * a.hidden;
+    const T* pair_row = static_cast<const T*>(a.pair_table) + static_cast<size_t>(pair) * a.hidden;
+    for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
+        const float value = __fadd_rn(__fmul_rn(to_float(row[i]), a.multiplier), to_float(pair_row[i]));
+        row_out[i] = value;
+        if (row_rounded) row_rounded[i] = from_float<RoundT>(value);
+    }
+}
+
+ME_EXPORT int me_pair_embedding(const void* table, const void* pair_table, int table_type, const int* ids,
+                                const int* entry_of_token, const int* cu_tokens, const int* state_slots,
+                                const int* fresh, int* last_token, float* out, void* rounded, int rounded_type,
+                                int tokens, int hidden, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                                float multiplier, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (buckets < 1 || mul_prev < 0 || mul_cur < 0) return ME_ERR_ARGUMENT;
+    PairEmbeddingArgs a{table, pair_table, ids, entry_of_token, cu_tokens, state_slots, fresh, last_token, out, rounded,
+                        hidden, vocab, buckets, mul_prev, mul_cur, multiplier};
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_type == ME_BF16) {
+        if (rounded_type == ME_BF16) return launch_kernel(pair_embedding_kernel<__nv_bfloat16, __nv_bfloat16>, tokens, threads, 0, stream, a);
+        return launch_kernel(pair_embedding_kernel<__nv_bfloat16, float>, tokens, threads, 0, stream, a);
+    }
+    if (rounded_type == ME_BF16) return launch_kernel(pair_embedding_kernel<float, __nv_bfloat16>, tokens, threads, 0, stream, a);
+    return launch_kernel(pair_embedding_kernel<float, float>, tokens, threads, 0, stream, a);
+}
+
+// ------------------------------------------------------------------------ float32 rows, rounded
+
+template <typename OutT>
+__global__ void round_rows_kernel(const float* __restrict__ x, OutT* __restrict__ out, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[idx] = from_float<OutT>(x[idx]);
+}
+
+// out = x in the compute dtype: the input of a sublayer that reads the residual stream itself.
+ME_EXPORT int me_round_rows(const float* x, void* out, int out_type, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t total = static_cast<size_t>(rows) * width;
+    const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
+    if (out_type == ME_BF16)
+        return launch_kernel(round_rows_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, static_cast<__nv_bfloat16*>(out), total);
+    return launch_kernel(round_rows_kernel<float>, blocks, 256, 0, stream, x, static_cast<float*>(out), total);
+}
+
+// ------------------------------------- norm over a whole projection + rotary + cache write + gates
+
+// One block per token over the columns of qkv = [q heads | k heads | v heads | gates].  Unlike the per-head
+// kernel above, q is normalised over all of its heads * head_dim columns at once with a weight of that size,
+// and k over its kv_heads * head_dim columns; then each head's first rotary_dim elements are rotated, q goes to
+// q_out and k, v to the token's cache slot (or to dense buffers).  `gates` trailing columns (one per query
+// head in the models that have them) leave the kernel as sigmoid(sum) in gate_out[t][gates], float32.
+// kv_heads == 0: a layer that reads another layer's keys and values has no k and v columns.
+struct WideQkvArgs {
+    const float* qkv;  // [splits][tokens][row_width]
+    int splits;
+    size_t split_stride;
+    int row_width;
+    const float* q_weight;  // [heads * head_dim] or null
+    const float* k_weight;  // [kv_heads * head_dim] or null
+    float eps;
+    const float2* cos_sin;  // [tokens][rotary_dim / 2] or null
+    const int* slot_mapping;
+    void* q_out;
+    void* k_pages;
+    void* v_pages;
+    void* k_dense;
+    void* v_dense;
+    float* gate_out;
+    int tokens, heads, kv_heads, head_dim, value_dim, page_size, rotary_dim, gates;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(256) qk_wide_norm_rope_store_kernel(WideQkvArgs a) {
+    extern __shared__ float row[];  // [row_width]
+    __shared__ float warp_partial[2][8];
+    const int token = blockIdx.x;
+    const int q_width = a.heads * a.head_dim, k_width = a.kv_heads * a.head_dim, v_width = a.kv_heads * a.value_dim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
+    const float* src = a.qkv + static_cast<size_t>(token) * a.row_width;
+    // Column i's square goes to the partial sum of thread i % 256, in ascending order: a token's
+    // statistics are the same bits in every step.
+    float q_sq = 0.0f, k_sq = 0.0f;
+    for (int i = threadIdx.x; i < a.row_width; i += 256) {
+        float v = 0.0f;
+        for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        row[i] = v;
+        if (i < q_width) q_sq = fmaf(v, v, q_sq);
+        else if (i < q_width + k_width) k_sq = fmaf(v, v, k_sq);
+    }
+    q_sq = warp_sum(q_sq), k_sq = warp_sum(k_sq);
+    if (lane == 0) warp_partial[0][warp] = q_sq, warp_partial[1][warp] = k_sq;
+    __syncthreads();
+    float q_total = 0.0f, k_total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) q_total += warp_partial[0][w], k_total += warp_partial[1][w];
+    const float q_inv = a.q_weight ? rsqrtf(q_total / static_cast<float>(q_width) + a.eps) : 1.0f;
+    const float k_inv = (a.k_weight && k_width) ? rsqrtf(k_total / static_cast<float>(k_width) + a.eps) : 1.0f;
+    const int half = a.rotary_dim / 2;
+    const float2* angles = a.cos_sin ? a.cos_sin + static_cast<size_t>(token) * half : nullptr;
+    const int slot = (a.slot_mapping && a.kv_heads) ? a.slot_mapping[token] : -1;
+    for (int i = threadIdx.x; i < a.row_width; i += 256) {
+        if (i < q_width + k_width) {
+            const bool is_q = i < q_width;
+            const int column = is_q ? i : i - q_width;
+            const int head = column / a.head_dim, e = column % a.head_dim;
+            const float* weight = is_q ? a.q_weight : a.k_weight;
+            const float inv = is_q ? q_inv : k_inv;
+            float value = weight ? weight[column] * (row[i] * inv) : row[i];
+            if (angles && e < a.rotary_dim) {
+                const int partner = e < half ? i + half : i - half;
+                const int partner_column = e < half ? column + half : column - half;
+                const float other = weight ? weight[partner_column] * (row[partner] * inv) : row[partner];
+                const float2 angle = angles[e < half ? e : e - half];
+                value = e < half ? value * angle.x - other * angle.y : value * angle.x + other * angle.y;
+            }
+            if (is_q) {
+                static_cast<OutT*>(a.q_out)[static_cast<size_t>(token) * q_width + column] = from_float<OutT>(value);
+            } else if (a.slot_mapping) {
+                if (slot >= 0) {
+                    const size_t page = slot / a.page_size, offset = slot % a.page_size;
+                    static_cast<OutT*>(a.k_pages)[((page * a.kv_heads + head) * a.page_size + offset) * a.head_dim + e] = from_float<OutT>(value);
+                }
+            } else {
+                static_cast<OutT*>(a.k_dense)[static_cast<size_t>(token) * k_width + column] = from_float<OutT>(value);
+            }
+        } else if (i < q_width + k_width + v_width) {
+            const int column = i - q_width - k_width;
+            const int head = column / a.value_dim, e = column % a.value_dim;
+            if (a.slot_mapping) {
+                if (slot >= 0) {
+                    const size_t page = slot / a.page_size, offset = slot % a.page_size;
+                    static_cast<OutT*>(a.v_pages)[((page * a.kv_heads + head) * a.page_size + offset) * a.value_dim + e] = from_float<OutT>(row[i]);
+                }
+            } else {
+                static_cast<OutT*>(a.v_dense)[static_cast<size_t>(token) * v_width + column] = from_float<OutT>(row[i]);
+            }
+        } else {
+            const int g = i - q_width - k_width - v_width;
+            if (g < a.gates) a.gate_out[static_cast<size_t>(token) * a.gates + g] = 1.0f / (1.0f + expf(-row[i]));
+        }
+    }
+}
+
+ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long split_stride, int row_width,
+                                         const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
+                                         const int* slot_mapping, void* q_out, void* k_pages, void* v_pages,
+                                         void* k_dense, void* v_dense, float* gate_out, int out_type, int tokens,
+                                         int heads, int kv_heads, int head_dim, int value_dim, int page_size,
+                                         int rotary_dim, int gates, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
+    if (row_width < (heads + kv_heads) * head_dim + kv_heads * value_dim + gates) return ME_ERR_ARGUMENT;
+    if (gates > 0 && gate_out == nullptr) return ME_ERR_ARGUMENT;
+    const size_t smem = static_cast<size_t>(row_width) * sizeof(float);
+    if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    WideQkvArgs a{qkv, splits, (size_t)split_stride, row_width, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin),
+                  slot_mapping, q_out, k_pages, v_pages, k_dense, v_dense, gate_out, tokens, heads, kv_heads, head_dim,
+                  value_dim, page_size, rotary_dim, gates};
+    if (out_type == ME_BF16) {
+        auto kernel = qk_wide_norm_rope_store_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch_kernel(kernel, tokens, 256, smem, stream, a);
+    }
+    auto kernel = qk_wide_norm_rope_store_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel(kernel, tokens, 256, smem, stream, a);
 }

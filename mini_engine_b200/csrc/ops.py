@@ -197,8 +197,14 @@ def add_rmsnorm(
     out: torch.Tensor,
     rows: torch.Tensor | None = None,
     pending_scale: torch.Tensor | None = None,
+    x_scale: float = 1.0,
+    keep_normed: bool = False,
 ) -> None:
     """``x += sum_s pending[s]`` (in place, float32) and ``out = weight * rmsnorm(x)``.
+
+    With ``x_scale`` the sum is ``x_scale * x + sum_s pending[s]``; with ``keep_normed`` it is the
+    normalised row (float32) that is written back to ``x`` instead of the sum (a layer whose norm
+    follows the sum).
 
     With ``rows`` only ``x[rows]`` (+ pending) are normalised into ``out[0..len(rows))`` and
     ``x`` is not modified.  With ``pending_scale`` (float32 ``[hidden]``) the sum that is added is
@@ -223,21 +229,24 @@ def add_rmsnorm(
     fn = _fn(
         "elementwise",
         "me_add_rmsnorm",
-        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_void_p],
     )
     code = fn(
         _ptr(x), _ptr(pending), splits, stride, _ptr(weight), eps, _ptr(out), _type_code(out.dtype),
-        _ptr(rows), count, hidden, _ptr(pending_scale), _stream(),
+        _ptr(rows), count, hidden, _ptr(pending_scale), float(x_scale), 1 if keep_normed else 0, _stream(),
     )  # fmt: skip
     _check(code, "add_rmsnorm")
 
 
 def swiglu(
-    partials: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0
+    partials: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0,
+    group_weight: torch.Tensor | None = None,
 ) -> None:
     """``out = g * sigmoid(slope * g) * (u + offset)`` where gate/up are the halves of ``sum_s
     partials[s]``, ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)`` when a limit is
-    given, else ``g = gate``, ``u = up``.  The defaults are ``silu(gate) * up``."""
+    given, else ``g = gate``, ``u = up``.  The defaults are ``silu(gate) * up``.  With ``group_weight``
+    (float32 ``[T, groups]``) the features form ``groups`` equal runs and feature ``i`` of token ``t`` is
+    multiplied by ``group_weight[t, i // (inter / groups)]`` (routed units side by side)."""
     _need(partials, torch.float32, "partials"), _need(out, None, "out")
     splits, tokens, width = partials.shape
     inter = width // 2
@@ -245,9 +254,15 @@ def swiglu(
         raise KernelError(f"swiglu: out {tuple(out.shape)} does not fit partials {tuple(partials.shape)}")
     if limit is not None and not limit > 0:
         raise KernelError("the limit of a gated activation must be positive (or absent)")
-    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    group_size = 0
+    if group_weight is not None:
+        _need(group_weight, torch.float32, "group_weight")
+        if group_weight.dim() != 2 or group_weight.shape[0] != tokens or inter % group_weight.shape[1]:
+            raise KernelError(f"swiglu: group_weight {tuple(group_weight.shape)} does not fit {tokens} tokens of {inter} features")
+        group_size = inter // group_weight.shape[1]
+    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_int, c_void_p])
     code = fn(_ptr(partials), splits, partials.stride(0), _ptr(out), _type_code(out.dtype), tokens, inter,
-              float(slope), float(limit or 0.0), float(offset), _stream())  # fmt: skip
+              float(slope), float(limit or 0.0), float(offset), _ptr(group_weight), group_size, _stream())  # fmt: skip
     _check(code, "swiglu")
 
 
@@ -378,20 +393,31 @@ def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor) -> None:
 
 
 def paged_attention_generic(
-    q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads, kv_heads, head_dim, scale, window
+    q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads, kv_heads, head_dim, scale, window,
+    value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
 ) -> None:
+    """One warp per (token, head), any head size; ``value_dim``: width of a value head when it differs;
+    ``sink``: one more participant of score zero and no value in the softmax; ``gate`` (float32 ``[T,
+    heads]``): a multiplier on each head's output."""
+    value_dim = head_dim if value_dim is None else value_dim
+    if gate is not None:
+        _need(gate, torch.float32, "gate")
+        if gate.shape != (q.shape[0], heads):
+            raise KernelError("gate must be [tokens, heads]")
+    if k_pages.shape[1:] != (kv_heads, k_pages.shape[2], head_dim) or v_pages.shape[1:] != (kv_heads, k_pages.shape[2], value_dim):
+        raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit the head sizes")
     _need(q, None, "q"), _need(out, q.dtype, "out"), _need(k_pages, q.dtype, "k_pages"), _need(v_pages, q.dtype, "v_pages")
     _need(block_table, torch.int32, "block_table"), _need(entry_of_token, torch.int32, "entry_of_token")
     _need(positions, torch.int32, "positions")
     fn = _fn(
         "attention_generic",
         "me_paged_attention_generic",
-        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 7 + [c_void_p],
+        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 9 + [c_void_p, c_void_p],
     )
     code = fn(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _ptr(entry_of_token), _ptr(positions), _ptr(out),
         _type_code(q.dtype), scale, q.shape[0], heads, kv_heads, head_dim, k_pages.shape[2], block_table.shape[1],
-        window, _stream(),
+        window, value_dim, 1 if sink else 0, _ptr(gate), _stream(),
     )  # fmt: skip
     _check(code, "paged_attention_generic")
 
@@ -563,6 +589,156 @@ def gla_finish(
         _type_code(out.dtype), tokens, heads, vdim, _stream(),
     )  # fmt: skip
     _check(code, "gla_finish")
+
+
+def pair_embedding(
+    *, table: torch.Tensor, pair_table: torch.Tensor, ctx, last_token: torch.Tensor, out: torch.Tensor,
+    rounded: torch.Tensor | None, multiplier: float, buckets: int, mul_prev: int, mul_cur: int,
+) -> None:  # fmt: skip
+    """``out[t] = table[id_t] * multiplier + pair_table[(previous id * mul_prev + id_t * mul_cur) mod buckets]`` in
+    float32 (row ``buckets`` of ``pair_table`` for a sequence's first token).  The id in front of an entry's first
+    token is read from ``last_token[slot]`` (int32 ``[slots + 1]``) unless the entry starts its sequence, and the
+    entry's last id is left there.  ``rounded``: the same rows in the compute dtype, or ``None``."""
+    _need(table, None, "table"), _need(pair_table, table.dtype, "pair_table"), _need(out, torch.float32, "out")
+    _need(last_token, torch.int32, "last_token")
+    vocab, hidden = table.shape
+    if pair_table.shape != (buckets + 1, hidden):
+        raise KernelError(f"pair_table {tuple(pair_table.shape)} is not [{buckets + 1}, {hidden}]")
+    if rounded is not None:
+        _need(rounded, None, "rounded")
+    fn = _fn("elementwise", "me_pair_embedding",
+             [c_void_p, c_void_p, c_int] + [c_void_p] * 8 + [c_int] * 5 + [c_longlong, c_longlong, c_float, c_void_p])  # fmt: skip
+    code = fn(
+        _ptr(table), _ptr(pair_table), _type_code(table.dtype), _ptr(ctx.token_ids), _ptr(ctx.entry_of_token),
+        _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(last_token), _ptr(out), _ptr(rounded),
+        _type_code(rounded.dtype) if rounded is not None else F32, out.shape[0], hidden, vocab, int(buckets),
+        int(mul_prev), int(mul_cur), float(multiplier), _stream(),
+    )  # fmt: skip
+    _check(code, "pair_embedding")
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x`` (float32 ``[T, width]``) in the dtype of ``out``."""
+    _need(x, torch.float32, "x"), _need(out, None, "out")
+    if out.shape != x.shape:
+        raise KernelError("round_rows: shapes differ")
+    fn = _fn("elementwise", "me_round_rows", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(out), _type_code(out.dtype), x.shape[0], x.shape[1], _stream()), "round_rows")
+
+
+def qk_wide_norm_rope_store(
+    *, qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int, value_dim: int, q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None, q_out: torch.Tensor, page_size: int,
+    slot_mapping: torch.Tensor | None = None, k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None,
+    k_dense: torch.Tensor | None = None, v_dense: torch.Tensor | None = None, gates: int = 0,
+    gate_out: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """RMSNorm of q over all its ``heads * head_dim`` columns at once (weight of that size) and of k over its
+    ``kv_heads * head_dim`` columns, rotation of the first ``rotary_dim`` elements of every head, and the write
+    of k and v to their cache slots (or dense buffers).  ``qkv`` is ``[S, T, width]`` float32 partial sums with the
+    columns ``[q | k | v | gates]``; the ``gates`` trailing columns come out as ``sigmoid`` in ``gate_out [T, gates]``."""
+    _need(qkv, torch.float32, "qkv"), _need(q_out, None, "q_out")
+    splits, tokens, width = qkv.shape
+    if width != (heads + kv_heads) * head_dim + kv_heads * value_dim + gates:
+        raise KernelError(f"qkv width {width} does not fit the head sizes and {gates} gates")
+    if kv_heads and slot_mapping is None and (k_dense is None or v_dense is None):
+        raise KernelError("either slot_mapping with pages or dense outputs must be given")
+    if kv_heads and slot_mapping is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+        if k_pages is None or v_pages is None or k_pages.dtype != q_out.dtype:
+            raise KernelError("pages must be given in the dtype of q_out")
+        if k_pages.shape[1:] != (kv_heads, page_size, head_dim) or v_pages.shape[1:] != (kv_heads, page_size, value_dim):
+            raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit kv_heads/page_size/head_dim")
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin")
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= head_dim:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= head_dim")
+    if q_weight is not None:
+        _need(q_weight, torch.float32, "q_weight")
+        if q_weight.shape != (heads * head_dim,):
+            raise KernelError("q_weight must have one value per column of q")
+    if k_weight is not None and kv_heads:
+        _need(k_weight, torch.float32, "k_weight")
+        if k_weight.shape != (kv_heads * head_dim,):
+            raise KernelError("k_weight must have one value per column of k")
+    if gates:
+        _need(gate_out, torch.float32, "gate_out")
+        if gate_out.shape != (tokens, gates):
+            raise KernelError("gate_out must be [tokens, gates]")
+    fn = _fn("elementwise", "me_qk_wide_norm_rope_store",
+             [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 8 + [c_int] * 9 + [c_void_p])  # fmt: skip
+    code = fn(
+        _ptr(qkv), splits, qkv.stride(0), width, _ptr(q_weight), _ptr(k_weight if kv_heads else None), float(eps),
+        _ptr(cos_sin), _ptr(slot_mapping if kv_heads else None), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(k_dense),
+        _ptr(v_dense), _ptr(gate_out), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, value_dim, page_size,
+        rotary_dim, gates, _stream(),
+    )  # fmt: skip
+    _check(code, "qk_wide_norm_rope_store")
+
+
+def rglru(
+    *, proj: torch.Tensor, in_bias: torch.Tensor, taps: torch.Tensor, conv_bias: torch.Tensor, ra_t: torch.Tensor,
+    ra_bias: torch.Tensor, ri_t: torch.Tensor, ri_bias: torch.Tensor, lam: torch.Tensor, ctx, state: torch.Tensor,
+    decay: torch.Tensor, driven: torch.Tensor, out: torch.Tensor, sharpness: float,
+) -> None:  # fmt: skip
+    """A gated linear recurrence per channel over the batch's tokens, entry by entry, from and into each request's
+    state slot.  ``proj`` is ``[S, T, 2 C]`` float32 partial sums (gate branch, then recurrent branch); ``taps [C, K]``
+    a causal convolution on the recurrent branch; ``ra_t``, ``ri_t`` ``[blocks, in, out]`` the two gates' block
+    matrices, transposed; ``state`` is ``[slots + 1, K, C]`` float32 (row 0 the recurrence, then the convolution's
+    last ``K - 1`` inputs); ``decay`` and ``driven`` are float32 scratch ``[T, C]``; ``out [T, C]`` is the state
+    times ``gelu_tanh`` of the gate branch in the compute dtype; ``sharpness`` is ``c`` of ``a = exp(-c r softplus(lam))``."""
+    for name, t in (("proj", proj), ("in_bias", in_bias), ("taps", taps), ("conv_bias", conv_bias), ("ra_t", ra_t),
+                    ("ra_bias", ra_bias), ("ri_t", ri_t), ("ri_bias", ri_bias), ("lam", lam), ("state", state),
+                    ("decay", decay), ("driven", driven)):  # fmt: skip
+        _need(t, torch.float32, name)
+    _need(out, None, "out")
+    splits, tokens, width = proj.shape
+    channels, taps_count = taps.shape
+    blocks = ra_t.shape[0]
+    block_width = channels // blocks
+    if width != 2 * channels or in_bias.shape != (width,) or channels % blocks:
+        raise KernelError("rglru: the projection must hold two branches of `channels` columns")
+    if ra_t.shape != (blocks, block_width, block_width) or ri_t.shape != ra_t.shape:
+        raise KernelError("rglru: the gates' matrices must be [blocks, channels / blocks, channels / blocks]")
+    for name, t in (("conv_bias", conv_bias), ("ra_bias", ra_bias), ("ri_bias", ri_bias), ("lam", lam)):
+        if t.shape != (channels,):
+            raise KernelError(f"rglru: {name} must have one value per channel")
+    if state.shape[1:] != (taps_count, channels) or out.shape != (tokens, channels):
+        raise KernelError("rglru: state must be [slots + 1, taps, channels] and out [tokens, channels]")
+    if decay.numel() < tokens * channels or driven.numel() < tokens * channels:
+        raise KernelError("rglru: scratch too small")
+    fn = _fn("recurrent", "me_rglru", [c_void_p, c_int, c_longlong] + [c_void_p] * 16 + [c_int] * 6 + [c_float, c_void_p])
+    code = fn(
+        _ptr(proj), splits, proj.stride(0), _ptr(in_bias), _ptr(taps), _ptr(conv_bias), _ptr(ra_t), _ptr(ra_bias),
+        _ptr(ri_t), _ptr(ri_bias), _ptr(lam), _ptr(ctx.entry_of_token), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots),
+        _ptr(ctx.fresh), _ptr(state), _ptr(decay), _ptr(driven), _ptr(out), _type_code(out.dtype), tokens,
+        ctx.num_entries, channels, blocks, taps_count, float(sharpness), _stream(),
+    )  # fmt: skip
+    _check(code, "rglru")
+
+
+def route(
+    *, h: torch.Tensor, router: torch.Tensor, weights: torch.Tensor, chosen: torch.Tensor, chosen_weight: torch.Tensor,
+    top: int, group_count: int, group_keep: int, weight_scale: float,
+) -> None:  # fmt: skip
+    """Per token the ``top`` units with the largest ``sigmoid(router h)`` among the units of the ``group_keep`` best
+    of ``group_count`` equal groups of neighbours (a group's value: the sum of its two largest scores); weights are
+    the chosen scores over their sum, times ``weight_scale``.  ``weights [T, units]`` float32 gets them densely (zero
+    elsewhere), ``chosen`` (int32) and ``chosen_weight`` (float32) ``[T, top]`` as lists."""
+    _need(h, None, "h"), _need(router, torch.float32, "router"), _need(weights, torch.float32, "weights")
+    _need(chosen, torch.int32, "chosen"), _need(chosen_weight, torch.float32, "chosen_weight")
+    tokens, hidden = h.shape
+    units = router.shape[0]
+    if router.shape != (units, hidden) or weights.shape != (tokens, units) or chosen.shape != (tokens, top) or chosen_weight.shape != (tokens, top):
+        raise KernelError("route: shapes do not fit")
+    fn = _fn("routing", "me_route", [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 6 + [c_float, c_void_p])
+    code = fn(
+        _ptr(h), _type_code(h.dtype), _ptr(router), _ptr(weights), _ptr(chosen), _ptr(chosen_weight), tokens, hidden,
+        units, int(top), int(group_count), int(group_keep), float(weight_scale), _stream(),
+    )  # fmt: skip
+    _check(code, "route")
 
 
 # --------------------------------------------------------------------------------- sampling

@@ -80,6 +80,7 @@ class ModelRunner:
         self.layout: CacheLayout = allocate_cache(
             model.cache_needs(), num_blocks, block_size, max_num_seqs, dtype, self.device,
             max_step_tokens=max_request_tokens or max_num_batched_tokens,
+            embedding_state=model.embedding_state(),
         )  # fmt: skip
         self.num_groups = len(self.layout.groups)
         self.workspace = Workspace(max_num_batched_tokens, self.device)
@@ -315,6 +316,7 @@ class ModelRunner:
                 "starts": starts + [0] * (total_entries - real),
                 "state_slots": [int(x) for x in state[:total_entries]],
             },
+            embedding_state=self.layout.embedding_state,
         )
         return ctx, at(o_rows, len(wanted_rows))
 

@@ -20,6 +20,14 @@ when ``p - j < window`` or ``j < keep_first``); a distance bias taken off the sc
 heads' softmax weights mixed by a learned ``[heads, heads]`` matrix before they meet the values
 (``talking_heads``: ``w'_h = sum_g T[h, g] w_g``, head ``h`` reads its own KV head with ``w'_h``).  The
 last four run in the kernels of ``csrc/attention_biased.cu``.
+
+Three more, for designs that normalise and gate differently: ``qk_norm_scope="projection"`` takes the
+root mean square of q over *all* its heads at once, and of k over all of its, with weights of that size
+(``"head"``, the default, is per head with one shared weight); ``softmax_sink`` adds a silent
+participant of score zero and no value to every softmax, ``p_j = exp(s_j) / (1 + sum_i exp(s_i))``;
+``head_gate`` multiplies head ``h``'s output by ``sigmoid(W_g x)_h`` with a learned ``W_g [heads,
+hidden]`` that runs as extra rows of the fused q/k/v product.  A layer that reads another entry's cache
+(``reads_shared_cache``) may have a window of its own.
 """
 
 from __future__ import annotations
@@ -65,6 +73,9 @@ class GroupedQueryAttention(Mixer):
         keep_first: int = 0,
         distance_bias: bool = False,
         talking_heads: bool = False,
+        qk_norm_scope: str = "head",
+        softmax_sink: bool = False,
+        head_gate: bool = False,
     ):
         if num_heads % kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of kv_heads ({kv_heads})")
@@ -72,12 +83,27 @@ class GroupedQueryAttention(Mixer):
         self.keep_first = int(keep_first) if window else 0
         self.distance_bias, self.talking_heads = bool(distance_bias), bool(talking_heads)
         # Whether the step runs in the kernels that know these options (any head size) or in the plain ones.
-        self.extended = bool(self.value_dim != head_dim or self.keep_first or distance_bias or talking_heads)
+        if qk_norm_scope not in ("head", "projection"):
+            raise ValueError(f"qk_norm_scope must be 'head' or 'projection', got {qk_norm_scope!r}")
+        self.wide_norm = qk_norm_scope == "projection" and qk_norm_eps is not None
+        self.sink, self.head_gate = bool(softmax_sink), bool(head_gate)
+        # Whether q, k, v (and the gates) leave the fused product through the kernel that normalises whole projections.
+        self.wide_store = self.wide_norm or self.head_gate
+        if self.head_gate and qk_norm_eps is not None and not self.wide_norm:
+            raise ValueError("head_gate comes with qk_norm_scope='projection' or without q/k norms")
+        if (self.wide_store or self.sink) and (keep_first or distance_bias or talking_heads or qkv_bias):
+            raise ValueError("qk_norm_scope='projection', softmax_sink and head_gate do not combine with keep_first, distance_bias, talking_heads or biases")
+        self.extended = bool(
+            (self.value_dim != head_dim and not (self.wide_store or self.sink)) or self.keep_first or distance_bias or talking_heads
+        )
         if self.extended:
             if reads_shared_cache or qkv_bias:
                 raise ValueError("the extended attention options do not combine with a shared cache or biases")
             if head_dim < 1 or self.value_dim < 1 or keep_first < 0:
                 raise ValueError("head sizes must be positive and keep_first must not be negative")
+        elif self.wide_store or self.sink:  # these run in the kernel that takes any head size
+            if not (1 <= head_dim <= 512 and 1 <= self.value_dim <= 512):
+                raise ValueError(f"head sizes must lie between 1 and 512, got {head_dim} and {self.value_dim}")
         else:
             ops.check_attention_sizes(head_dim, num_heads, kv_heads)
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden_size, num_heads, kv_heads, head_dim
@@ -105,6 +131,7 @@ class GroupedQueryAttention(Mixer):
             "r1": "distance_bias.r1",
             "r2": "distance_bias.r2",
             "talk": "talking_heads.weight",
+            "gate": "gate_proj.weight",
         }
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
         self.position = None
@@ -136,10 +163,13 @@ class GroupedQueryAttention(Mixer):
             specs += [WeightSpec(n[key], (self.heads,), role="vector", init="positive") for key in ("r1", "r2")]
         if self.talking_heads:
             specs.append(WeightSpec(n["talk"], (self.heads, self.heads), role="vector", init="ones_normal"))
+        if self.head_gate:
+            specs.append(WeightSpec(n["gate"], (self.heads, self.hidden)))
         if self.qk_norm_eps is not None:
-            specs.append(WeightSpec(n["q_norm"], (d,), role="vector", init="ones_normal"))
+            q_len, k_len = (self.heads * d, self.kv_heads * d) if self.wide_norm else (d, d)
+            specs.append(WeightSpec(n["q_norm"], (q_len,), role="vector", init="ones_normal"))
             if not self.reads_shared_cache:
-                specs.append(WeightSpec(n["k_norm"], (d,), role="vector", init="ones_normal"))
+                specs.append(WeightSpec(n["k_norm"], (k_len,), role="vector", init="ones_normal"))
         if self.qkv_bias:
             specs.append(WeightSpec(n["q_bias"], (self.heads * d,), role="vector"))
             if not self.reads_shared_cache:
@@ -152,6 +182,8 @@ class GroupedQueryAttention(Mixer):
         rows = [tensors[n["q"]]]
         if not self.reads_shared_cache:
             rows += [tensors[n["k"]], tensors[n["v"]]]
+        if self.head_gate:
+            rows.append(tensors[n["gate"]])
         self.qkv = Linear(torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0])
         self.out = Linear(tensors[n["o"]])
         if self.qk_norm_eps is not None:
@@ -178,6 +210,8 @@ class GroupedQueryAttention(Mixer):
         q = ctx.buffer("attn.q", (tokens, self.heads * d), ctx.dtype)
         table = self.position.step_angles(ctx) if self.position is not None else None
         slots = ctx.slot_mapping[cache.group]
+        if self.wide_store or self.sink:
+            return self._forward_gated(qkv, q, table, slots, ctx, cache)
         args: dict[str, Any] = dict(
             qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, q_weight=self.q_norm,
             k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, positions=ctx.positions, q_out=q,
@@ -233,5 +267,37 @@ class GroupedQueryAttention(Mixer):
             q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx,
             out=out, heads=self.heads, kv_heads=self.kv_heads, head_dim=d, scale=self.scale,
             window=self.window or 0,
+        )  # fmt: skip
+        return self.out.forward(out, ctx, "attn.o")
+
+    def _forward_gated(self, qkv, q, table, slots, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        """The step with a projection-wide norm, a sink in the softmax or gated heads."""
+        tokens, d = q.shape[0], self.head_dim
+        kv_in = 0 if self.reads_shared_cache else self.kv_heads
+        if self.position is not None and table is None:
+            raise ValueError("these attention options take a rotation that the fused kernel applies, or none")
+        gate = ctx.buffer("attn.gate", (tokens, self.heads), torch.float32) if self.head_gate else None
+        if self.wide_store:
+            args: dict[str, Any] = dict(
+                qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, value_dim=self.value_dim, q_weight=self.q_norm,
+                k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, cos_sin=table, q_out=q, page_size=ctx.page_size,
+                gates=self.heads if self.head_gate else 0, gate_out=gate,
+            )  # fmt: skip
+            if kv_in and not cache.writes:  # this execution reads another entry's cache: its own keys and values are not kept
+                unused_k = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
+                unused_v = ctx.buffer("attn.v_new", (tokens, kv_in * self.value_dim), ctx.dtype)
+                ops.qk_wide_norm_rope_store(**args, k_dense=unused_k, v_dense=unused_v)
+            else:
+                ops.qk_wide_norm_rope_store(**args, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v)
+        else:
+            ops.qk_norm_rope_store(
+                qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, q_weight=self.q_norm, k_weight=self.k_norm,
+                eps=self.qk_norm_eps or 0.0, positions=ctx.positions, q_out=q, page_size=ctx.page_size, cos_sin=table,
+                value_dim=self.value_dim, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v,
+            )  # fmt: skip
+        out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
+        ops.paged_attention_generic(
+            q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.entry_of_token, ctx.positions, out, self.heads,
+            self.kv_heads, d, self.scale, self.window or 0, value_dim=self.value_dim, sink=self.sink, gate=gate,
         )  # fmt: skip
         return self.out.forward(out, ctx, "attn.o")

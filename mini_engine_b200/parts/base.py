@@ -72,12 +72,15 @@ class Residual:
     ``pending`` is ``None`` or a float32 tensor ``[S, T, hidden]`` whose ``S`` slices (the
     partial sums of a split matrix product) are all still to be added to ``x``; with
     ``pending_scale`` (float32 ``[hidden]``, a layer scale) their sum is multiplied column by column
-    before it is added.
+    before it is added.  ``rounded`` is ``x`` in the compute dtype when a part has already made that
+    copy (an embedding, or a norm that wrote its result back to ``x``), for a sublayer that reads the
+    stream itself; whoever changes ``x`` sets or clears it.
     """
 
     x: torch.Tensor
     pending: torch.Tensor | None = None
     pending_scale: torch.Tensor | None = None
+    rounded: torch.Tensor | None = None
 
     def add(self, delta: torch.Tensor, scale: torch.Tensor | None = None) -> None:
         if self.pending is not None:
@@ -137,6 +140,7 @@ class StepContext:
     decode_entries: torch.Tensor | None = None  # ... their numbers, ascending (int32)
     portion_entries: torch.Tensor | None = None  # the numbers of the entries that bring more
     host: Mapping[str, Any] = field(default_factory=dict)  # host copies for parts written in Python
+    embedding_state: torch.Tensor | None = None  # [slots + 1, *shape]: per-request state of the embedding part
     memo: dict = field(default_factory=dict)  # what parts compute once per step and share between layers
 
     def buffer(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -167,11 +171,19 @@ class Part:
 
 class Norm(Part):
     def forward(
-        self, state: Residual, ctx: StepContext, out_dtype: torch.dtype, rows: torch.Tensor | None = None
+        self,
+        state: Residual,
+        ctx: StepContext,
+        out_dtype: torch.dtype,
+        rows: torch.Tensor | None = None,
+        residual_scale: float = 1.0,
+        keep_normed: bool = False,
     ) -> torch.Tensor:
         """Add ``state.pending`` into ``state.x`` (and clear it), return the normalised rows
         in ``out_dtype``.  With ``rows`` (int32 ``[N]``) only those rows are produced, as
-        ``[N, hidden]``, and ``state.x`` is left as it was."""
+        ``[N, hidden]``, and ``state.x`` is left as it was.  ``residual_scale`` multiplies ``state.x``
+        before the pending output is added; with ``keep_normed`` the normalised rows (float32) replace
+        ``state.x`` (an arrangement whose norm follows the sum)."""
         raise NotImplementedError
 
 
@@ -216,8 +228,14 @@ class FeedForward(Part):
 class Embedding(Part):
     """The model's first part: token ids to rows of the residual stream."""
 
-    def forward(self, token_ids: torch.Tensor, ctx: StepContext, out: torch.Tensor) -> None:
-        """Fill ``out [T, hidden]`` (float32, the residual stream) for ``token_ids [T]`` (int32)."""
+    def state(self) -> StateSpec | None:
+        """Per-request state of fixed size that the embedding keeps between steps (``ctx.embedding_state``,
+        indexed by the request's state slot), or ``None``."""
+        return None
+
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, out: torch.Tensor) -> torch.Tensor | None:
+        """Fill ``out [T, hidden]`` (float32, the residual stream) for ``token_ids [T]`` (int32).  May
+        return the same rows in the compute dtype when it has made them on the way."""
         raise NotImplementedError
 
 

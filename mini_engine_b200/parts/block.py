@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import Block, LayerCache, Residual, StepContext, register
 from mini_engine_b200.weights.loader import WeightSpec
 
@@ -76,5 +77,48 @@ class ScaledPreNormBlock(Block):
 @register("block", "prenorm_scaled_mixer_only")
 class ScaledMixerOnlyBlock(ScaledPreNormBlock):
     """The same arrangement for a layer without a feed-forward: one norm, one layer scale."""
+
+    NORMS = ("mixer",)
+
+
+@register("block", "postnorm")
+class PostNormBlock(Block):
+    """The norm follows the sum: ``x = norm_m(alpha * x + mixer(x))``, then ``x = norm_f(alpha * x +
+    feed_forward(x))``.  The sublayers read the stream itself (rounded to the compute dtype); each sum, in
+    32-bit, and its norm are one kernel, which leaves the normalised row as the new stream."""
+
+    capturable = True
+
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str, hidden_size: int, alpha: float = 1.0, unused_names=()):
+        """``alpha``: what the stream is multiplied by before a sublayer's output is added.  ``unused_names``:
+        tensors of the layer that a checkpoint may carry although the layer has no use for them."""
+        super().__init__(mixer, feed_forward, norms)
+        self.alpha = float(alpha)
+        self.unused = [prefix + name for name in unused_names]
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return super().weight_specs() + [WeightSpec(name, (), role="vector", optional=True) for name in self.unused]
+
+    @staticmethod
+    def _stream(state: Residual, ctx: StepContext) -> torch.Tensor:
+        """The stream in the compute dtype."""
+        if ctx.dtype == torch.float32:
+            return state.x
+        if state.rounded is None:
+            state.rounded = ctx.buffer("block.rounded", tuple(state.x.shape), ctx.dtype)
+            ops.round_rows(state.x, state.rounded)
+        return state.rounded
+
+    def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
+        state.add(self.mixer.forward(self._stream(state, ctx), ctx, cache))
+        self.mixer_norm.forward(state, ctx, ctx.dtype, residual_scale=self.alpha, keep_normed=True)
+        if self.feed_forward is not None:
+            state.add(self.feed_forward.forward(self._stream(state, ctx), ctx))
+            self.feed_forward_norm.forward(state, ctx, ctx.dtype, residual_scale=self.alpha, keep_normed=True)
+
+
+@register("block", "postnorm_mixer_only")
+class PostNormMixerOnlyBlock(PostNormBlock):
+    """The same arrangement for a layer without a feed-forward: one norm."""
 
     NORMS = ("mixer",)

@@ -28,7 +28,7 @@ from mini_engine_b200.parts.base import (
 from mini_engine_b200.weights.loader import WeightSpec
 
 # Importing the built-in parts registers them.
-from mini_engine_b200.parts import attention, block, ends, linear_attention, mlp, norms, parallel, rotary  # noqa: F401,E402
+from mini_engine_b200.parts import attention, block, ends, linear_attention, mlp, moe, norms, parallel, recurrent, rotary  # noqa: F401,E402
 
 
 def build_block(spec: ModelSpec, index: int) -> Block:
@@ -95,6 +95,10 @@ class DecoderModel:
             needs.append((mixer.paged_cache(), mixer.state(), entry.cache_of))
         return needs
 
+    def embedding_state(self) -> StateSpec | None:
+        """The per-request state that the embedding part keeps, if any."""
+        return self.embedding.state()
+
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.embedding.load(tensors)
         for blk in self.blocks:
@@ -112,8 +116,8 @@ class DecoderModel:
 
     def _forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:
         x = ctx.buffer("residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
-        self.embedding.forward(ctx.token_ids, ctx, x)
         state = Residual(x)
+        state.rounded = self.embedding.forward(ctx.token_ids, ctx, x)
         for entry, cache in zip(self.spec.order, caches, strict=True):
             self.blocks[entry.layer].forward(state, ctx, cache)
         count = logits_rows.shape[0]

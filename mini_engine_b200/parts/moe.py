@@ -1,0 +1,104 @@
+"""A feed-forward made of many small gated units ("experts") of which every token uses a few.
+
+Router: ``s = sigmoid(W_r h)`` in 32-bit.  The units form ``group_count`` equal groups of neighbours; a group is
+valued by the sum of its two largest scores and only units of the ``group_keep`` best groups are eligible; the
+``top`` eligible units with the largest scores are chosen, with weights ``s / (sum of the chosen s + 1e-20) *
+weight_scale``.  Unit ``e``: ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``, ``W_down (g *
+sigmoid(gate_slope * g) * (u + up_offset))`` (the constants of :mod:`~mini_engine_b200.parts.mlp`).  The output is
+the weighted sum of the chosen units' outputs.
+
+How it runs: all units' gate and up matrices are one row-concatenated weight and all down matrices one
+column-concatenated weight.  A routing kernel leaves a dense map ``[T, units]`` of weights (zero for units that a
+token did not choose); the activation kernel multiplies every unit's features by its weight for the token; the
+down product then *is* the weighted sum over the chosen units.  The step has no shape that depends on the choice,
+so it can be captured in a graph, and a token's result does not depend on the rest of the batch.  The price is the
+arithmetic of the units that a token did not choose, which matters for prompts when ``top`` is a small part of
+``units`` (a step of few tokens reads nearly all units' weights anyway).
+"""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from mini_engine_b200.csrc import ops
+from mini_engine_b200.parts.base import FeedForward, StepContext, register
+from mini_engine_b200.parts.linear import Linear
+from mini_engine_b200.weights.loader import WeightSpec
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    capturable = True
+
+    def __init__(
+        self,
+        prefix: str,
+        hidden_size: int,
+        *,
+        units: int,
+        top: int,
+        intermediate_size: int,
+        group_count: int = 1,
+        group_keep: int = 1,
+        weight_scale: float = 1.0,
+        gate_slope: float = 1.0,
+        limit: float | None = None,
+        up_offset: float = 0.0,
+        names: Mapping[str, str] | None = None,
+    ):
+        if min(units, top, intermediate_size, group_count, group_keep) < 1:
+            raise ValueError("routed_experts: sizes must be positive")
+        if units % group_count or group_keep > group_count or top > group_keep * (units // group_count):
+            raise ValueError(
+                f"routed_experts: {units} units do not form {group_count} equal groups of which {group_keep} hold {top} choices"
+            )
+        if limit is not None and not limit > 0:
+            raise ValueError(f"the limit of the gated unit must be positive, got {limit}")
+        self.hidden, self.units, self.top, self.inter = hidden_size, units, top, intermediate_size
+        self.group_count, self.group_keep, self.weight_scale = group_count, group_keep, float(weight_scale)
+        self.gate_slope, self.limit, self.up_offset = float(gate_slope), limit, float(up_offset)
+        defaults = {"router": "router.weight", "unit": "experts.{index}.", "gate": "gate_proj.weight",
+                    "up": "up_proj.weight", "down": "down_proj.weight"}  # fmt: skip
+        self.names = {key: (names or {}).get(key, value) for key, value in defaults.items()}
+        self.prefix = prefix
+        self.gate_up: Linear | None = None
+        self.down: Linear | None = None
+        self.router: torch.Tensor | None = None
+
+    def _name(self, unit: int, which: str) -> str:
+        return self.prefix + self.names["unit"].format(index=unit) + self.names[which]
+
+    def weight_specs(self) -> list[WeightSpec]:
+        specs = []
+        for unit in range(self.units):
+            specs += [
+                WeightSpec(self._name(unit, "gate"), (self.inter, self.hidden)),
+                WeightSpec(self._name(unit, "up"), (self.inter, self.hidden)),
+                WeightSpec(self._name(unit, "down"), (self.hidden, self.inter)),
+            ]
+        # the router is applied in 32-bit
+        specs.append(WeightSpec(self.prefix + self.names["router"], (self.units, self.hidden), role="vector", init="small_normal"))
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        gates = [tensors[self._name(unit, "gate")] for unit in range(self.units)]
+        ups = [tensors[self._name(unit, "up")] for unit in range(self.units)]
+        self.gate_up = Linear(torch.cat(gates + ups, dim=0).contiguous())  # [all gates | all ups]
+        self.down = Linear(torch.cat([tensors[self._name(unit, "down")] for unit in range(self.units)], dim=1).contiguous())
+        self.router = tensors[self.prefix + self.names["router"]]
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        tokens = h.shape[0]
+        weights = ctx.buffer("routed.weights", (tokens, self.units), torch.float32)
+        chosen = ctx.buffer("routed.chosen", (tokens, self.top), torch.int32)
+        chosen_weight = ctx.buffer("routed.chosen_weight", (tokens, self.top), torch.float32)
+        ops.route(
+            h=h, router=self.router, weights=weights, chosen=chosen, chosen_weight=chosen_weight, top=self.top,
+            group_count=self.group_count, group_keep=self.group_keep, weight_scale=self.weight_scale,
+        )  # fmt: skip
+        both = self.gate_up.forward(h, ctx, "routed.gate_up")
+        act = ctx.buffer("routed.act", (tokens, self.units * self.inter), ctx.dtype)
+        ops.swiglu(both, act, self.gate_slope, self.limit, self.up_offset, group_weight=weights)
+        return self.down.forward(act, ctx, "routed.down")

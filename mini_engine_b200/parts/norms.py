@@ -42,10 +42,15 @@ class RMSNorm(Norm):
         if self.offset != 0.0:
             self.weight = (self.weight + self.offset).contiguous()
 
-    def forward(self, state: Residual, ctx: StepContext, out_dtype, rows=None) -> torch.Tensor:
+    def forward(
+        self, state: Residual, ctx: StepContext, out_dtype, rows=None, residual_scale: float = 1.0, keep_normed: bool = False
+    ) -> torch.Tensor:
         count = state.x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm.out" if rows is None else "norm.rows", (count, self.dim), out_dtype)
-        ops.add_rmsnorm(state.x, state.pending, self.weight, self.eps, out, rows, state.pending_scale)
+        ops.add_rmsnorm(
+            state.x, state.pending, self.weight, self.eps, out, rows, state.pending_scale, residual_scale, keep_normed
+        )
         if rows is None:
             state.clear()
+            state.rounded = out if keep_normed else None  # with keep_normed, `out` is the new stream, rounded
         return out
