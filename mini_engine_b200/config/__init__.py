@@ -2,6 +2,7 @@
 
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
+from mini_engine_b200.config.molotar import MolotarConfig
 from mini_engine_b200.config.pimezen import PimezenConfig
 from mini_engine_b200.config.qwen3 import Qwen3Config
 from mini_engine_b200.config.registry import (
@@ -19,6 +20,7 @@ __all__ = [
     "ModelSpec",
     "OrderEntry",
     "PartSpec",
+    "MolotarConfig",
     "PimezenConfig",
     "Qwen3Config",
     "architecture_for",

@@ -45,7 +45,7 @@ def embed(tokens: list[int], cfg: dict, w: dict, dtype=torch.float64) -> torch.T
 def rotary_frequencies(rot: dict) -> list[float]:
     """``f_i = base^(-2i/R)``, then stretched by wavelength: short waves stay, long ones are divided by
     ``factor``, and those between are blended linearly in ``original / wavelength``."""
-    dims, base, sc = rot["dims"], rot["base"], rot.get("scaling")
+    dims, base, sc = rot["dims"], rot["base"], rot.get("scaling")  # sc may be None: plain frequencies
     out = []
     for i in range(dims // 2):
         f = base ** (-2.0 * i / dims)
@@ -82,29 +82,40 @@ def attention_keys_values(h: torch.Tensor, m: dict, w: dict, p: str, eps: float)
     G, d, e = m["kv_heads"], m["dim"], m["vdim"]
     k = h @ w[p + "k"].to(h.dtype).T
     k = rms_norm(k, w[p + "k.norm"], eps).view(T, G, d)
-    k = rotate(k, list(range(T)), m["rot"])
+    if m.get("rot"):
+        k = rotate(k, list(range(T)), m["rot"])
     v = (h @ w[p + "v"].to(h.dtype).T).view(T, G, e)
     return k, v
+
+
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int | None) -> torch.Tensor:
+    """``q [T, H, d]``, ``k [T, G, d]``, ``v [T, G, e]`` of one sequence -> ``[T, H, e]``.  Query i sees keys j with
+    ``0 <= i - j < window``; the weights are ``exp(s_j) / (1 + sum exp(s))``: a silent participant of score zero."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        for i in range(T):
+            lo = 0 if window is None else max(0, i - window + 1)
+            s = (k[lo : i + 1, g] @ q[i, head]) * scale
+            weights = torch.exp(s) / (1.0 + torch.exp(s).sum())
+            out[i, head] = (weights[:, None] * v[lo : i + 1, g]).sum(dim=0)
+    return out
 
 
 def attention(h: torch.Tensor, m: dict, w: dict, p: str, eps: float, kv=None):
     """Windowed grouped-query attention whose softmax has one more, silent participant of score zero,
     with a sigmoid gate per head on the way out.  ``kv``: keys and values of another layer to use."""
     T = h.shape[0]
-    H, G, d, e, W = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+    H, d, e = m["heads"], m["dim"], m["vdim"]
+    window = m["mask"]["size"] if m.get("mask") else None
     q = h @ w[p + "q"].to(h.dtype).T
     q = rms_norm(q, w[p + "q.norm"], eps).view(T, H, d)
-    q = rotate(q, list(range(T)), m["rot"])
+    if m.get("rot"):
+        q = rotate(q, list(range(T)), m["rot"])
     k, v = kv if kv is not None else attention_keys_values(h, m, w, p, eps)
     gate = torch.sigmoid(h @ w[p + "g"].to(h.dtype).T)  # [T, H]
-    out = torch.zeros(T, H, e, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        for i in range(T):
-            lo = max(0, i - W + 1)
-            s = (k[lo : i + 1, g] @ q[i, head]) * m["scale"]
-            weights = torch.exp(s) / (1.0 + torch.exp(s).sum())
-            out[i, head] = (weights[:, None] * v[lo : i + 1, g]).sum(dim=0) * gate[i, head]
+    out = attend(q, k, v, m["scale"], window) * gate[:, :, None]
     return out.reshape(T, H * e) @ w[p + "o"].to(h.dtype).T, (k, v)
 
 
@@ -147,7 +158,7 @@ def route(h: torch.Tensor, router: dict, weight: torch.Tensor):
     """Per token: chosen experts and their weights.  Sigmoid scores; experts in equal groups of neighbours, a
     group valued by its two best scores, only the best groups eligible; the chosen scores normalised."""
     E, top = router["experts"], router["top"]
-    count, keep = router["groups"]["count"], router["groups"]["keep"]
+    count, keep = (router["groups"]["count"], router["groups"]["keep"]) if router.get("groups") else (1, 1)
     scores = torch.sigmoid(h @ weight.to(h.dtype).T)  # [T, E]
     chosen, weights = [], []
     for s in scores:
