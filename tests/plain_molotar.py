@@ -126,7 +126,7 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor) -> torc
     """Per channel: ``out_t = bias + sum_j taps[:, K-1-j] * x_(t-j)``; nothing before the start."""
     T, K = x.shape[0], taps.shape[1]
     out = bias.to(x.dtype).expand(T, -1).clone()
-    for j in range(K):
+    for j in range(min(K, T)):
         out[j:] += x[: T - j] * taps[:, K - 1 - j].to(x.dtype)
     return out
 
@@ -154,23 +154,39 @@ def rglru(h: torch.Tensor, m: dict, w: dict, p: str) -> torch.Tensor:
 # --------------------------------------------------------------------------- routed feed-forward
 
 
-def route(h: torch.Tensor, router: dict, weight: torch.Tensor):
-    """Per token: chosen experts and their weights.  Sigmoid scores; experts in equal groups of neighbours, a
-    group valued by its two best scores, only the best groups eligible; the chosen scores normalised."""
+def route(h: torch.Tensor, router: dict, weight: torch.Tensor, follow: dict | None = None, close: float = 0.0):
+    """Per token: chosen experts, their weights, and how close the choice was.  Sigmoid scores; experts in equal
+    groups of neighbours, a group valued by its two best scores, only the best groups eligible; the chosen scores
+    normalised.  The third result is the smallest gap by which a group or an expert won its place.
+
+    ``follow`` (token -> experts) is somebody else's choice: where it differs from the one made here it is taken
+    instead, provided the decision here was closer than ``close`` (a choice with a tiny gap may fall the other way
+    under rounding, and everything behind it then follows the other choice); a differing choice on a clear
+    decision is an error."""
     E, top = router["experts"], router["top"]
     count, keep = (router["groups"]["count"], router["groups"]["keep"]) if router.get("groups") else (1, 1)
     scores = torch.sigmoid(h @ weight.to(h.dtype).T)  # [T, E]
-    chosen, weights = [], []
-    for s in scores:
+    chosen, weights, gaps = [], [], []
+    for t, s in enumerate(scores):
         per = E // count
         value = [sum(sorted(s[g * per : (g + 1) * per].tolist(), reverse=True)[:2]) for g in range(count)]
-        groups = sorted(range(count), key=lambda g: (-value[g], g))[:keep]
-        allowed = [x for g in groups for x in range(g * per, (g + 1) * per)]
-        pick = sorted(allowed, key=lambda x: (-float(s[x]), x))[:top]
+        ranked = sorted(range(count), key=lambda g: (-value[g], g))
+        groups = ranked[:keep]
+        allowed = sorted((x for g in groups for x in range(g * per, (g + 1) * per)), key=lambda x: (-float(s[x]), x))
+        pick = allowed[:top]
+        gap = float("inf")
+        if keep < count:
+            gap = min(gap, value[ranked[keep - 1]] - value[ranked[keep]])
+        if top < len(allowed):
+            gap = min(gap, float(s[allowed[top - 1]]) - float(s[allowed[top]]))
+        if follow is not None and sorted(follow[t]) != sorted(pick):
+            assert gap < close, f"token {t}: {sorted(follow[t])} chosen where {sorted(pick)} wins by {gap:.4f}"
+            pick = list(follow[t])
         total = sum(float(s[x]) for x in pick) + 1e-20
         chosen.append(pick)
         weights.append([float(s[x]) / total * router["scale"] for x in pick])
-    return chosen, weights
+        gaps.append(gap)
+    return chosen, weights, gaps
 
 
 def expert(h: torch.Tensor, w: dict, p: str, limit: float) -> torch.Tensor:
@@ -179,8 +195,11 @@ def expert(h: torch.Tensor, w: dict, p: str, limit: float) -> torch.Tensor:
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].to(h.dtype).T
 
 
-def moe(h: torch.Tensor, mlp: dict, w: dict, p: str) -> torch.Tensor:
-    chosen, weights = route(h, mlp["router"], w[p + "router"])
+def moe(h: torch.Tensor, mlp: dict, w: dict, p: str, gaps: list | None = None, follow: dict | None = None, close: float = 0.0) -> torch.Tensor:
+    """``gaps`` (optional) collects, per call, every token's closest routing decision; ``follow``, ``close``: see :func:`route`."""
+    chosen, weights, closest = route(h, mlp["router"], w[p + "router"], follow, close)
+    if gaps is not None:
+        gaps.append(closest)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for x, weight in zip(chosen[t], weights[t]):
@@ -191,9 +210,11 @@ def moe(h: torch.Tensor, mlp: dict, w: dict, p: str) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------- model
 
 
-def forward(tokens: list[int], cfg: dict, w: dict, dtype=torch.float64):
+def forward(tokens: list[int], cfg: dict, w: dict, dtype=torch.float64, gaps: list | None = None, follow: dict | None = None, close: float = 0.0):
     """Logits ``[T, vocab]`` and the stream after every layer ``[layers, T, D]``.  A layer is
-    ``x = norm1(alpha x + mixer(x))``, ``x = norm2(alpha x + ff(x))``: the norm follows the sum."""
+    ``x = norm1(alpha x + mixer(x))``, ``x = norm2(alpha x + ff(x))``: the norm follows the sum.
+    ``follow``: per routed feed-forward (counted from 0 in layer order) and token, a choice to follow (:func:`route`)."""
+    routed = 0
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     x = embed(tokens, cfg, w, dtype)
     kept, after = {}, []
@@ -209,7 +230,9 @@ def forward(tokens: list[int], cfg: dict, w: dict, dtype=torch.float64):
             raise ValueError(layer["type"])
         x = rms_norm(alpha * x + mixed, w[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = rms_norm(alpha * x + moe(x, layer["mlp"], w, p + "mlp."), w[p + "norm2"], eps)
+            chosen = None if follow is None else follow[routed]
+            routed += 1
+            x = rms_norm(alpha * x + moe(x, layer["mlp"], w, p + "mlp.", gaps, chosen, close), w[p + "norm2"], eps)
         after.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].to(dtype).T
     return logits, torch.stack(after)
