@@ -1,6 +1,7 @@
-"""Prefill and decode throughput of the Pimezen design beside Qwen3 dense at equal layer sizes.
+"""Prefill and decode throughput of another design (Pimezen, Molotar) beside Qwen3 dense at equal layer sizes.
 
-    python -m mini_engine_b200.cli.design_bench [--sizes 1b,8b] [--steps K] [--warmup W]      (or: bench.py --design pimezen)
+    python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar] [--sizes 1b,8b] [--steps K] [--warmup W]
+    (or: bench.py --design pimezen|molotar)
 
 For each size both models get the same width, feed-forward width, head counts, head size, layer count
 and vocabulary, seeded random bfloat16 weights, and the same two workloads: one prompt of 2,048 tokens
@@ -10,6 +11,12 @@ linear attention has as many heads.  Beside the step times, every kernel class i
 prompt step and one eager decode step (CUDA events around each launch) and set against its roofline: the
 longer of (algorithmic bytes / measured copy bandwidth) and (algorithmic flops / measured bfloat16 peak)
 over the time it took.  One JSON line is printed.
+
+Molotar gets four layers in the order attention, recurrence, recurrence, attention that reads the first layer's keys
+and values; its attention has Qwen3's head counts and head size, a window of 1,024 tokens and half of each head
+rotated; its recurrence is as wide as the model with blocks of 128 channels and four taps; its feed-forward has 8
+units in 4 groups of which 2 are kept, a token uses 2 units, and a unit is half as wide as Qwen3's feed-forward, so
+that a token uses as many feed-forward weights as in Qwen3 while the layer holds four times as many.
 """
 
 from __future__ import annotations
@@ -30,10 +37,32 @@ SIZES = {
     "8b": dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=4, vocab=32768, lin_dim=128, lin_vdim=128, rank=64),
 }
 TIMED = ("biased_attention", "mixed_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
-         "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding")  # fmt: skip
+         "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding", "rglru", "route",
+         "qk_wide_norm_rope_store", "pair_embedding", "round_rows")  # fmt: skip
+UNITS, UNITS_USED, UNIT_GROUPS, UNIT_GROUPS_KEPT = 8, 2, 4, 2
+RECURRENCE_BLOCK, RECURRENCE_TAPS = 128, 4
 
 
-def configs(size: dict):
+def molotar_config(size: dict):
+    from mini_engine_b200.config import MolotarConfig
+
+    d = size["head_dim"]
+    attention = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": d**-0.5,
+                 "mask": {"size": WINDOW},
+                 "rot": {"dims": d // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}  # fmt: skip
+    recurrence = {"width": size["width"], "blocks": size["width"] // RECURRENCE_BLOCK, "conv": RECURRENCE_TAPS}
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"] // UNITS_USED, "limit": 7.0},
+           "router": {"experts": UNITS, "top": UNITS_USED, "scale": 1.0, "groups": {"count": UNIT_GROUPS, "keep": UNIT_GROUPS_KEPT}}}  # fmt: skip
+    pattern = [("attention", attention), ("rglru", recurrence), ("rglru", recurrence), ("attention", {**attention, "kv_from": 0})]
+    layers = [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer in (pattern * size["layers"])[: size["layers"]]]
+    return MolotarConfig.from_dict({
+        "architecture": "Molotar", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+        "embedding": {"scale": size["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+        "layers": layers,
+    })  # fmt: skip
+
+
+def configs(size: dict, design: str = "pimezen"):
     from mini_engine_b200.config import PimezenConfig, Qwen3Config
 
     qwen = Qwen3Config(
@@ -53,6 +82,8 @@ def configs(size: dict):
     }  # fmt: skip
     pimezen = PimezenConfig.from_dict({"architecture": "Pimezen", "vocab": size["vocab"], "width": size["width"],
                                        "norm": {"eps": 1e-6}, "layers": [layer] * size["layers"]})  # fmt: skip
+    if design == "molotar":
+        return {"molotar": molotar_config(size), "qwen3": qwen}
     return {"pimezen": pimezen, "qwen3": qwen}
 
 
@@ -116,7 +147,7 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
     def bound(name, nbytes, nflops):
         out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
 
-    window = WINDOW if design == "pimezen" else None
+    window = WINDOW if design in ("pimezen", "molotar") else None
     keep = KEEP_FIRST if design == "pimezen" else 0
     seen_prompt = visible_sum(0, PROMPT, window, keep)
     seen_decode = BATCH * visible_sum(CONTEXT, CONTEXT + 1, window, keep)
@@ -130,6 +161,33 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
         row = (2 * h * ld + h * lv + rank) * 4
         bound("prompt.gla_scan", PROMPT * (row + h * lv * 4) + 2 * state, PROMPT * h * ld * lv * 4)
         bound("decode.gla_scan", BATCH * (8 * row + h * lv * 4 + 2 * state), BATCH * h * ld * lv * 4)
+    # The products of a layer (averaged over the layers): a prompt is bound by the flops of the weights a token uses,
+    # a decode step by the bytes of the weights that the batch touches.
+    width, ff = size["width"], size["ff"]
+    if design == "molotar":
+        c = width  # channels of the recurrence
+        mixers = [width * (h * d + 2 * g * d + h) + h * d * width, 3 * width * c, 3 * width * c, width * (h * d + h) + h * d * width]
+        mixer = sum(mixers) / len(mixers)
+        unit = 3 * width * (ff // UNITS_USED)
+        used = UNITS_USED * unit
+        touched = UNITS * (1.0 - (1.0 - UNITS_USED / UNITS) ** BATCH) * unit
+        bound("prompt.gemm_tensor_core", (mixer + UNITS * unit) * 2, 2 * PROMPT * (mixer + used))
+        bound("decode.gemm_tensor_core", (mixer + touched) * 2, 2 * BATCH * (mixer + used))
+        # the recurrence: the projections' sums in, the decay and the driven term out and in again, the gated state out
+        gates = 2 * c * RECURRENCE_BLOCK
+        bound("prompt.rglru", PROMPT * c * (2 * 4 + 4 * 4 + 2) + gates * 4, 2 * PROMPT * gates)
+        bound("decode.rglru", BATCH * c * (2 * 4 + 4 * 4 + 2 + 2 * RECURRENCE_TAPS * 4) + gates * 4, 2 * BATCH * gates)
+        # kernel times are averaged over all layers, of which half have an attention and half a recurrence
+        for name in ("prompt.paged_attention", "decode.paged_attention", "prompt.rglru", "decode.rglru"):
+            out[name] = {key: value * 0.5 for key, value in out[name].items()}
+    elif design == "qwen3":
+        mixer = width * (h * d + 2 * g * d) + h * d * width
+        dense = 3 * width * ff
+        for phase, tokens, names in (("prompt", PROMPT, ("gemm_tensor_core", "gemm_tensor_core_swiglu")),
+                                     ("decode", BATCH, ("gemm_tensor_core", "gemm_tensor_core_swiglu"))):  # fmt: skip
+            out[f"{phase}.products"] = {"bytes": (mixer + dense) * 2, "flops": 2 * tokens * (mixer + dense),
+                                        "roofline_us": max((mixer + dense) * 2 / bw, 2 * tokens * (mixer + dense) / flops) * 1e6,
+                                        "kernels": names}  # fmt: skip
     return out
 
 
@@ -221,6 +279,11 @@ def run_design(design: str, cfg, size: dict, steps: int, warmup: int, peaks: dic
                 record["roofline_us"] = round(bound["roofline_us"], 3)
                 record["of_roofline"] = round(bound["roofline_us"] / per_layer, 4)
             kernels[f"{phase}.{name}"] = record
+        combined = bounds.get(f"{phase}.products")
+        if combined:  # all products of a layer against one bound (gated and plain ones are separate kernel classes)
+            spent = sum(totals.get(name, 0.0) for name in combined["kernels"]) / layers
+            kernels[f"{phase}.products"] = {"us_per_layer": round(spent, 2), "roofline_us": round(combined["roofline_us"], 3),
+                                            "of_roofline": round(combined["roofline_us"] / spent, 4) if spent else None}  # fmt: skip
     return {
         "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(PROMPT / prefill_ms * 1e3, 1),
         "decode_ms_per_step": round(decode_ms, 4), "decode_tokens_per_s": round(BATCH / decode_ms * 1e3, 1),
@@ -240,7 +303,7 @@ def layer_weight_bytes(model, layers: int) -> int:
     return total // layers
 
 
-def run(sizes: list[str], steps: int, warmup: int) -> dict:
+def run(sizes: list[str], steps: int, warmup: int, design: str = "pimezen") -> dict:
     import torch
 
     peaks_file = ROOT / "MEASURED_PEAKS.json"
@@ -248,26 +311,27 @@ def run(sizes: list[str], steps: int, warmup: int) -> dict:
     if peaks_file.is_file():
         raw = json.loads(peaks_file.read_text())
         peaks = {"hbm_gbs": float(raw.get("hbm_gbs", 6650.0)), "bf16_tflops": float(raw.get("bf16_tflops", 1590.0)), "source": "measured"}
-    out = {"metric": "prefill and decode throughput of Pimezen beside Qwen3 dense at equal layer sizes", "dtype": "bf16",
+    out = {"metric": f"prefill and decode throughput of {design.capitalize()} beside Qwen3 dense at equal layer sizes", "dtype": "bf16",
            "data": "synthetic", "workload": {"prompt_tokens": PROMPT, "decode_batch": BATCH, "decode_context": CONTEXT,
                                              "window": WINDOW, "keep_first": KEEP_FIRST, "steps": steps, "warmup": warmup},
            "peaks": peaks, "sizes": {}}  # fmt: skip
     for name in sizes:
         size = SIZES[name]
         out["sizes"][name] = {"config": size}
-        for design, cfg in configs(size).items():
-            out["sizes"][name][design] = run_design(design, cfg, size, steps, warmup, peaks)
+        for which, cfg in configs(size, design).items():
+            out["sizes"][name][which] = run_design(which, cfg, size, steps, warmup, peaks)
             torch.cuda.empty_cache()
     return out
 
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--design", choices=["pimezen", "molotar"], default="pimezen")
     parser.add_argument("--sizes", default="1b,8b")
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=5)
     args = parser.parse_args(argv)
-    print(json.dumps(run(args.sizes.split(","), args.steps, max(args.warmup, 3))))
+    print(json.dumps(run(args.sizes.split(","), args.steps, max(args.warmup, 3), args.design)))
     return 0
 
 

@@ -47,7 +47,12 @@ struct AttnParams {
     int heads, kv_heads, page_size, table_width, window, max_splits;
     int page_shift;  // log2(page_size) when it is a power of two, else -1
     int tiles_per_cta;  // decode: consecutive 128-key tiles that one CTA walks
+    int sink = 0;       // 1: the softmax has one more participant of score zero and no value (denominator + exp(-max))
+    const float* gate = nullptr;  // [tokens][heads] multiplier of each head's output, or null
 };
+
+// What the silent participant adds to a denominator that is relative to `max_log2` (scores in the log2 domain).
+__device__ __forceinline__ float sink_term(const AttnParams& p, float max_log2) { return p.sink ? exp2f(-max_log2) : 0.0f; }
 
 // ------------------------------------------------------------------------ small helpers
 
@@ -293,7 +298,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + (lane >> 2) + r * 8;
         if (row >= rows_valid) continue;
-        const float inv = 1.0f / row_sum[r];
+        float inv = 1.0f / (row_sum[r] + sink_term(p, row_max[r]));
+        if (p.gate) inv *= p.gate[static_cast<size_t>(token0 + q_block * BLOCK_M + row) * p.heads + head];
         __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * BLOCK_M + row) * p.heads + head) * D;
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
@@ -544,7 +550,8 @@ __device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int h
     }
     const int token = p.cu_tokens[entry];
     __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
-    const float inv = 1.0f / denom;
+    float inv = 1.0f / (denom + sink_term(p, total_max));
+    if (p.gate) inv *= p.gate[static_cast<size_t>(token) * p.heads + head];
 #pragma unroll
     for (int i = 0; i < PER_LANE; i += 2)
         *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(value[i] * inv, value[i + 1] * inv);
@@ -857,8 +864,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const int head = kv_head * group + row;
         if (!direct)
             p.partials[((static_cast<size_t>(entry) * p.heads + head) * p.max_splits + split) * STRIDE + col] = value;
-        else if (col < D)
-            p.out[(static_cast<size_t>(token) * p.heads + head) * D + col] = __float2bfloat16(value / denom);
+        else if (col < D) {
+            float result = value / (denom + sink_term(p, total_max));
+            if (p.gate) result *= p.gate[static_cast<size_t>(token) * p.heads + head];
+            p.out[(static_cast<size_t>(token) * p.heads + head) * D + col] = __float2bfloat16(result);
+        }
     }
     if (direct || p.counters == nullptr) return;  // nothing to merge, or a separate kernel merges
 
@@ -950,13 +960,13 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
                                          const int* cu_tokens, const int* context_lens, void* out, float scale,
                                          int entries, int max_new_tokens, int heads, int kv_heads, int head_dim,
                                          int page_size, int table_width, int window, const int* entry_ids,
-                                         cudaStream_t stream) {
+                                         int sink, const float* gate, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), nullptr, nullptr, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, 0, shift_of(page_size), 1};
+                 page_size, table_width, window, 0, shift_of(page_size), 1, sink, gate};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
@@ -971,14 +981,15 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                                              const int* block_table, const int* cu_tokens, const int* context_lens,
                                              void* out, float* partials, int* counters, float scale, int entries, int max_splits,
                                              int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
-                                             int table_width, int window, const int* entry_ids, cudaStream_t stream) {
+                                             int table_width, int window, const int* entry_ids, int sink,
+                                             const float* gate, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
     if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta};
+                 page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta, sink, gate};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 
@@ -993,7 +1004,7 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
                                            const int* cu_tokens, const int* context_lens, void* out, float* partials,
                                            int* counters, float scale, int entries, int splits, int warps, int heads,
                                            int kv_heads, int head_dim, int page_size, int table_width, int window,
-                                           const int* entry_ids, cudaStream_t stream) {
+                                           const int* entry_ids, int sink, const float* gate, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 8) return ME_ERR_UNSUPPORTED;
     if (shift_of(page_size) < 3) return ME_ERR_UNSUPPORTED;
@@ -1001,7 +1012,7 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
     if (warps != 8 && warps != 6) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), nullptr, nullptr, block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, splits, shift_of(page_size), 0};
+                 page_size, table_width, window, splits, shift_of(page_size), 0, sink, gate};
     CUtensorMap maps[2];
     memcpy(&maps[0], k_map, sizeof(CUtensorMap));
     memcpy(&maps[1], v_map, sizeof(CUtensorMap));
@@ -1029,7 +1040,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                                        int page_size, int table_width, int window, cudaStream_t stream) {
     return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
                                           nullptr, scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
-                                          table_width, window, nullptr, stream);
+                                          table_width, window, nullptr, 0, nullptr, stream);
 }
 
 // ------------------------------------------------- decode attention without allocation

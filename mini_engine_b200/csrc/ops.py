@@ -423,19 +423,22 @@ def paged_attention_generic(
 
 
 def paged_attention(
-    *, q, k_pages, v_pages, block_table, ctx, out, heads: int, kv_heads: int, head_dim: int, scale: float, window: int
-) -> None:
+    *, q, k_pages, v_pages, block_table, ctx, out, heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
+    value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
+) -> None:  # fmt: skip
     """Causal attention of the batch's new tokens over their requests' cached keys (the new
-    tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes."""
-    if q.dtype == torch.bfloat16:
+    tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes.  ``value_dim``,
+    ``sink`` and ``gate`` as in :func:`paged_attention_generic`; value heads of another width than the key
+    heads take that kernel."""
+    if q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
-                q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window
+                q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate
             )
             return
     paged_attention_generic(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,
-        scale, window,
+        scale, window, value_dim=value_dim, sink=sink, gate=gate,
     )  # fmt: skip
 
 

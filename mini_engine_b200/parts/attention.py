@@ -296,8 +296,9 @@ class GroupedQueryAttention(Mixer):
                 value_dim=self.value_dim, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v,
             )  # fmt: skip
         out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
-        ops.paged_attention_generic(
-            q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.entry_of_token, ctx.positions, out, self.heads,
-            self.kv_heads, d, self.scale, self.window or 0, value_dim=self.value_dim, sink=self.sink, gate=gate,
+        ops.paged_attention(
+            q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx, out=out,
+            heads=self.heads, kv_heads=self.kv_heads, head_dim=d, scale=self.scale, window=self.window or 0,
+            value_dim=self.value_dim, sink=self.sink, gate=gate,
         )  # fmt: skip
         return self.out.forward(out, ctx, "attn.o")

@@ -64,15 +64,16 @@ CONFIG_S = {
     ],
 }  # fmt: skip
 # Widths that the tensor-core products take, windows that straddle pages of 16, an attention layer without a window
-# and one without rotation, a bigram table of one bucket, alpha 1.
+# and without rotation whose heads (64 wide, keys and values alike) the tensor-core attention kernels take in bfloat16,
+# read again by a later layer with a window; a bigram table of one bucket, alpha 1.
 CONFIG_T = {
     "architecture": "Molotar", "vocab": 64, "width": 64, "norm": {"eps": 1e-6}, "postln_alpha": 1.0,
     "embedding": {"scale": 1.0, "bigram": {"buckets": 1, "mul_prev": 1, "mul_cur": 1}},
     "layers": [
         {"type": "attention", "mixer": attention(8, 2, 32, 32, 0.18, 33, ROT_B), "mlp": routed(64, 1.0, 4, 1, 1.0, 2, 1)},
-        {"type": "attention", "mixer": attention(2, 1, 64, 48, 0.125, None, None), "mlp": routed(32, 2.0, 8, 2, 2.0, 8, 4)},
+        {"type": "attention", "mixer": attention(2, 1, 64, 64, 0.125, None, None), "mlp": routed(32, 2.0, 8, 2, 2.0, 8, 4)},
         {"type": "rglru", "mixer": {"width": 128, "blocks": 4, "conv": 4}, "mlp": routed(64, 1.5, 2, 2, 0.5, 1, 1)},
-        {"type": "attention", "mixer": attention(4, 1, 64, 48, 0.125, 16, None, kv_from=1), "mlp": None},
+        {"type": "attention", "mixer": attention(4, 1, 64, 64, 0.125, 16, None, kv_from=1), "mlp": None},
     ],
 }  # fmt: skip
 # Sizes that no fast path takes: a width that is no multiple of 8, odd head widths, one head, a window of one token,
@@ -383,6 +384,59 @@ def test_a_key_that_stands_out_at_the_windows_edge(window, offset, dtype_name):
         assert (row[0, 0] > 50.0) == visible, f"the marked value is {'missing' if visible else 'seen'}"
         tolerance = 2e-5 if dtype_name == "float32" else 2e-2
         assert torch.allclose(got, want[positions], atol=tolerance * 100.0, rtol=tolerance)
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("heads,kv_heads,page", [(4, 2, 8), (8, 1, 16), (12, 1, 16), (4, 4, 4)])
+@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7]])
+@pytest.mark.parametrize("window", [0, 70])
+def test_tensor_core_attention_with_a_silent_participant_and_gates(head_dim, heads, kv_heads, page, news, window):
+    """The bfloat16 kernels on tensor cores (prompt portions; decode by TMA for groups up to 8 and pages from 8
+    tokens, else the tiled one; mixed steps) with the silent participant and the gates, against float64."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import attention_bf16, ops
+
+    g = torch.Generator().manual_seed(head_dim + heads + page + len(news) + window)
+    lengths = [400, 90, 130, 300]
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    k_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    v_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    table = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    q_rows, want_rows, gate_rows, entry_of, positions = [], [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        q = (0.5 * torch.randn(n, heads, head_dim, generator=g)).to(torch.bfloat16)
+        k = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        v = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        if b % 2:
+            q = -q.abs()  # scores mostly far below zero: the silent participant holds most of the weight
+            k = k.abs()
+        gate = torch.rand(n, heads, generator=g)
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+        for p in range(n):
+            k_pages[table[b, p // page], :, p % page] = k[p]
+            v_pages[table[b, p // page], :, p % page] = v[p]
+        want = plain.attend(q.double(), k.double(), v.double(), head_dim**-0.5, window or None) * gate.double()[:, :, None]
+        q_rows.append(q[n - new :]), want_rows.append(want[n - new :]), gate_rows.append(gate[n - new :])
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    data = dict(new_counts=news, lengths=lengths, entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda())  # fmt: skip
+    q_all = torch.cat(q_rows).reshape(-1, heads * head_dim).contiguous().cuda()
+    want = torch.cat(want_rows).reshape(-1, heads * head_dim).float()
+    out = torch.full_like(q_all, float("nan"))
+    assert attention_bf16.supports(head_dim, heads, kv_heads)
+    ops.paged_attention(
+        q=q_all, k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), block_table=table.cuda(), ctx=fake_context(data), out=out,
+        heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=head_dim**-0.5, window=window, sink=True,
+        gate=torch.cat(gate_rows).contiguous().cuda(),
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert attention_bf16.take_error() == 0
+    error = float((out.float().cpu() - want).abs().max()) / float(want.abs().max())
+    assert error < 1.5e-2, error
 
 
 def test_norm_over_whole_projections_rotation_gates_and_cache_write():
