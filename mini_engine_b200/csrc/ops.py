@@ -684,17 +684,17 @@ def qk_wide_norm_rope_store(
 def rglru(
     *, proj: torch.Tensor, in_bias: torch.Tensor, taps: torch.Tensor, conv_bias: torch.Tensor, ra_t: torch.Tensor,
     ra_bias: torch.Tensor, ri_t: torch.Tensor, ri_bias: torch.Tensor, lam: torch.Tensor, ctx, state: torch.Tensor,
-    decay: torch.Tensor, driven: torch.Tensor, out: torch.Tensor, sharpness: float,
+    decay: torch.Tensor, driven: torch.Tensor, conv: torch.Tensor, out: torch.Tensor, sharpness: float,
 ) -> None:  # fmt: skip
     """A gated linear recurrence per channel over the batch's tokens, entry by entry, from and into each request's
     state slot.  ``proj`` is ``[S, T, 2 C]`` float32 partial sums (gate branch, then recurrent branch); ``taps [C, K]``
     a causal convolution on the recurrent branch; ``ra_t``, ``ri_t`` ``[blocks, in, out]`` the two gates' block
     matrices, transposed; ``state`` is ``[slots + 1, K, C]`` float32 (row 0 the recurrence, then the convolution's
-    last ``K - 1`` inputs); ``decay`` and ``driven`` are float32 scratch ``[T, C]``; ``out [T, C]`` is the state
+    last ``K - 1`` inputs); ``decay``, ``driven`` and ``conv`` are float32 scratch ``[T, C]``; ``out [T, C]`` is the state
     times ``gelu_tanh`` of the gate branch in the compute dtype; ``sharpness`` is ``c`` of ``a = exp(-c r softplus(lam))``."""
     for name, t in (("proj", proj), ("in_bias", in_bias), ("taps", taps), ("conv_bias", conv_bias), ("ra_t", ra_t),
                     ("ra_bias", ra_bias), ("ri_t", ri_t), ("ri_bias", ri_bias), ("lam", lam), ("state", state),
-                    ("decay", decay), ("driven", driven)):  # fmt: skip
+                    ("decay", decay), ("driven", driven), ("conv", conv)):  # fmt: skip
         _need(t, torch.float32, name)
     _need(out, None, "out")
     splits, tokens, width = proj.shape
@@ -710,13 +710,13 @@ def rglru(
             raise KernelError(f"rglru: {name} must have one value per channel")
     if state.shape[1:] != (taps_count, channels) or out.shape != (tokens, channels):
         raise KernelError("rglru: state must be [slots + 1, taps, channels] and out [tokens, channels]")
-    if decay.numel() < tokens * channels or driven.numel() < tokens * channels:
+    if min(decay.numel(), driven.numel(), conv.numel()) < tokens * channels:
         raise KernelError("rglru: scratch too small")
-    fn = _fn("recurrent", "me_rglru", [c_void_p, c_int, c_longlong] + [c_void_p] * 16 + [c_int] * 6 + [c_float, c_void_p])
+    fn = _fn("recurrent", "me_rglru", [c_void_p, c_int, c_longlong] + [c_void_p] * 17 + [c_int] * 6 + [c_float, c_void_p])
     code = fn(
         _ptr(proj), splits, proj.stride(0), _ptr(in_bias), _ptr(taps), _ptr(conv_bias), _ptr(ra_t), _ptr(ra_bias),
         _ptr(ri_t), _ptr(ri_bias), _ptr(lam), _ptr(ctx.entry_of_token), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots),
-        _ptr(ctx.fresh), _ptr(state), _ptr(decay), _ptr(driven), _ptr(out), _type_code(out.dtype), tokens,
+        _ptr(ctx.fresh), _ptr(state), _ptr(decay), _ptr(driven), _ptr(conv), _ptr(out), _type_code(out.dtype), tokens,
         ctx.num_entries, channels, blocks, taps_count, float(sharpness), _stream(),
     )  # fmt: skip
     _check(code, "rglru")

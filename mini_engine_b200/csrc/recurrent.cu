@@ -15,18 +15,20 @@
 // `[K][C]` floats: row 0 is S, rows 1 .. K-1 the last K-1 inputs x of the convolution, oldest first.  An entry
 // that starts its sequence starts from zeros.
 //
-// Two kernels.  `gates`: a CTA takes 8 tokens of one block, forms their u in shared memory (the convolution
-// reaches back into the entry's earlier tokens of this step or into the state) and 128 channels' two gates,
-// reading each weight once for the 8 tokens; it leaves a_t and the driven term in scratch.  `scan`: a thread
-// per (entry, channel) walks the entry's tokens in order, then leaves S and the convolution's history in the
+// Three kernels.  `conv`: a thread per (token, channel) forms u (the convolution reaches back into the entry's
+// earlier tokens of this step or into the state) and leaves it in scratch.  `gates`: a CTA takes 16 tokens of one
+// block, holds their u in shared memory and forms 64 channels' two gates, reading each weight once for the 16
+// tokens; it leaves a_t and the driven term in scratch.  `scan`: a CTA per
+// (entry, 32 channels) walks the entry's tokens in order, then leaves S and the convolution's history in the
 // slot.  A token's arithmetic is the same whatever the step holds, so float32 results do not depend on the cut.
 #include "common.cuh"
 
 #include <algorithm>
 
-constexpr int GATE_TOKENS = 8;
-constexpr int GATE_THREADS = 128;
-constexpr int SCAN_THREADS = 128;
+constexpr int GATE_TOKENS = 16;
+constexpr int GATE_THREADS = 64;
+constexpr int SCAN_WARPS = 8;   // warps of a scan CTA: all fetch, one walks
+constexpr int SCAN_TILE = 64;   // tokens that a scan CTA holds in shared memory at a time
 constexpr int MAX_TAPS = 16;
 
 struct RecurrentArgs {
@@ -48,6 +50,7 @@ struct RecurrentArgs {
     float* state;   // [slots + 1][K][channels]
     float* decay;   // scratch [tokens][channels]: a_t
     float* driven;  // scratch [tokens][channels]: sqrt(1 - a_t^2) i_t u_t
+    float* conv;    // scratch [tokens][channels]: u_t
     void* out;      // [tokens][channels]
     int tokens, entries, channels, blocks, taps_count;
     float sharpness;  // c of a_t = exp(-c r_t softplus(lam))
@@ -61,32 +64,41 @@ __device__ __forceinline__ float branch_input(const RecurrentArgs& a, int t, int
     return v + a.in_bias[column];
 }
 
+__global__ void __launch_bounds__(256) rglru_conv_kernel(RecurrentArgs a) {
+    const int K = a.taps_count;
+    const size_t total = static_cast<size_t>(a.tokens) * a.channels;
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(idx / a.channels), c = static_cast<int>(idx % a.channels);
+        const int entry = a.entry_of_token[t];
+        const int n = t - a.cu_tokens[entry];  // tokens of this entry in front of t
+        const float* history = a.fresh[entry] ? nullptr : a.state + (static_cast<size_t>(a.state_slots[entry]) * K + 1) * a.channels;
+        float u = a.conv_bias[c];
+        for (int back = 0; back < K; ++back) {
+            float x = 0.0f;
+            if (n - back >= 0) x = branch_input(a, t - back, a.channels + c);
+            else if (history) x = history[static_cast<size_t>(n - back + K - 1) * a.channels + c];
+            u = fmaf(a.taps[static_cast<size_t>(c) * K + (K - 1 - back)], x, u);
+        }
+        a.conv[idx] = u;
+    }
+}
+
 __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs a) {
     extern __shared__ float u_tile[];  // [GATE_TOKENS][block_width]
     const int width = a.channels / a.blocks;
     const int chunks = (width + GATE_THREADS - 1) / GATE_THREADS;
     const int block = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
     const int first_token = blockIdx.x * GATE_TOKENS;
-    const int K = a.taps_count;
     pdl_trigger();
     pdl_wait();
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < GATE_TOKENS * width; idx += GATE_THREADS) {
         const int tok = idx / width, j = idx % width;
-        const int t = first_token + tok, c = block * width + j;
-        float u = 0.0f;
-        if (t < a.tokens) {
-            const int entry = a.entry_of_token[t];
-            const int n = t - a.cu_tokens[entry];  // tokens of this entry in front of t
-            const float* history = a.fresh[entry] ? nullptr : a.state + (static_cast<size_t>(a.state_slots[entry]) * K + 1) * a.channels;
-            u = a.conv_bias[c];
-            for (int back = 0; back < K; ++back) {
-                float x = 0.0f;
-                if (n - back >= 0) x = branch_input(a, t - back, a.channels + c);
-                else if (history) x = history[static_cast<size_t>(n - back + K - 1) * a.channels + c];
-                u = fmaf(a.taps[static_cast<size_t>(c) * K + (K - 1 - back)], x, u);
-            }
-        }
-        u_tile[idx] = u;
+        const int t = first_token + tok;
+        u_tile[idx] = t < a.tokens ? a.conv[static_cast<size_t>(t) * a.channels + block * width + j] : 0.0f;
     }
     __syncthreads();
     const int k = chunk * GATE_THREADS + threadIdx.x;
@@ -97,6 +109,7 @@ __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs
     for (int tok = 0; tok < GATE_TOKENS; ++tok) r[tok] = a.ra_bias[c], g[tok] = a.ri_bias[c];
     const float* wr = a.ra_t + static_cast<size_t>(block) * width * width + k;
     const float* wi = a.ri_t + static_cast<size_t>(block) * width * width + k;
+#pragma unroll 8
     for (int j = 0; j < width; ++j) {
         const float r_weight = wr[static_cast<size_t>(j) * width], i_weight = wi[static_cast<size_t>(j) * width];
 #pragma unroll
@@ -124,11 +137,17 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// A CTA owns 32 channels of one entry.  Its eight warps fetch a tile of 64 tokens (decay, driven term, gate
+// branch) while the tile before is being worked on, and apply the gate's activation; warp 0 alone then walks the
+// tile in order, one channel per lane, which is all that is serial: one multiply-add per token.
 template <typename OutT>
-__global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(RecurrentArgs a) {
-    const int c = blockIdx.x * SCAN_THREADS + threadIdx.x;
+__global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_kernel(RecurrentArgs a) {
+    __shared__ float s_decay[SCAN_TILE][32], s_state[SCAN_TILE][32], s_gate[SCAN_TILE][32];
+    constexpr int PER_THREAD = SCAN_TILE / SCAN_WARPS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 32 + lane;
+    const bool live = c < a.channels;
     const int entry = blockIdx.y;
-    if (c >= a.channels) return;
     const int K = a.taps_count;
     pdl_trigger();
     pdl_wait();
@@ -136,21 +155,67 @@ __global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(RecurrentArgs 
     const int count = end - begin;
     float* slot = a.state + static_cast<size_t>(a.state_slots[entry]) * K * a.channels;
     const bool fresh = a.fresh[entry] != 0;
-    float state = fresh ? 0.0f : slot[c];
+    float state = 0.0f;
     float history[MAX_TAPS - 1];
 #pragma unroll
-    for (int i = 0; i < MAX_TAPS - 1; ++i) history[i] = (i < K - 1 && !fresh) ? slot[static_cast<size_t>(1 + i) * a.channels + c] : 0.0f;
-    OutT* out = static_cast<OutT*>(a.out);
-    const float gate_bias = a.in_bias[c];
-#pragma unroll 4
-    for (int t = begin; t < end; ++t) {
-        const size_t at = static_cast<size_t>(t) * a.channels + c;
-        state = fmaf(a.decay[at], state, a.driven[at]);
-        const float* gate_src = a.proj + static_cast<size_t>(t) * 2 * a.channels + c;
-        float gate = 0.0f;
-        for (int s = 0; s < a.splits; ++s) gate += gate_src[s * a.split_stride];
-        out[at] = from_float<OutT>(state * gelu_tanh(gate + gate_bias));
+    for (int i = 0; i < MAX_TAPS - 1; ++i) history[i] = 0.0f;
+    if (warp == 0 && live && !fresh) {
+        state = slot[c];
+#pragma unroll
+        for (int i = 0; i < MAX_TAPS - 1; ++i)
+            if (i < K - 1) history[i] = slot[static_cast<size_t>(1 + i) * a.channels + c];
     }
+    OutT* out = static_cast<OutT*>(a.out);
+    const float gate_bias = live ? a.in_bias[c] : 0.0f;
+    float r_decay[PER_THREAD], r_driven[PER_THREAD], r_gate[PER_THREAD];
+    // All loads of a tile are issued before any is used: the partial sums are walked split by split, not token by token.
+    auto fetch = [&](int tile_begin) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int t = tile_begin + warp + i * SCAN_WARPS;
+            const bool there = t < end && live;
+            const size_t at = static_cast<size_t>(there ? t : begin) * a.channels + (live ? c : 0);
+            r_decay[i] = there ? a.decay[at] : 0.0f;
+            r_driven[i] = there ? a.driven[at] : 0.0f;
+            r_gate[i] = 0.0f;
+        }
+        for (int s = 0; s < a.splits; ++s) {
+#pragma unroll
+            for (int i = 0; i < PER_THREAD; ++i) {
+                const int t = tile_begin + warp + i * SCAN_WARPS;
+                if (t < end && live) r_gate[i] += a.proj[s * a.split_stride + static_cast<size_t>(t) * 2 * a.channels + c];
+            }
+        }
+    };
+    fetch(begin);
+    for (int tile_begin = begin; tile_begin < end; tile_begin += SCAN_TILE) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int tok = warp + i * SCAN_WARPS;
+            s_decay[tok][lane] = r_decay[i];
+            s_state[tok][lane] = r_driven[i];
+            s_gate[tok][lane] = gelu_tanh(r_gate[i] + gate_bias);
+        }
+        __syncthreads();
+        fetch(tile_begin + SCAN_TILE);  // the next tile's loads are in flight under the serial walk
+        const int n = min(SCAN_TILE, end - tile_begin);
+        if (warp == 0) {
+#pragma unroll 8
+            for (int tok = 0; tok < n; ++tok) {
+                state = fmaf(s_decay[tok][lane], state, s_state[tok][lane]);
+                s_state[tok][lane] = state;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int tok = warp + i * SCAN_WARPS;
+            if (tok < n && live)
+                out[static_cast<size_t>(tile_begin + tok) * a.channels + c] = from_float<OutT>(s_state[tok][lane] * s_gate[tok][lane]);
+        }
+        __syncthreads();
+    }
+    if (warp != 0 || !live) return;
     slot[c] = state;
     // The convolution's history after this entry: the inputs of the sequence's last K - 1 positions, of which
     // the entry brought the last `count` (or all of them).
@@ -176,7 +241,8 @@ static SharedMemoryOptIn g_gates_opt_in;
 ME_EXPORT int me_rglru(const float* proj, int splits, long long split_stride, const float* in_bias, const float* taps,
                        const float* conv_bias, const float* ra_t, const float* ra_bias, const float* ri_t,
                        const float* ri_bias, const float* lam, const int* entry_of_token, const int* cu_tokens,
-                       const int* state_slots, const int* fresh, float* state, float* decay, float* driven, void* out,
+                       const int* state_slots, const int* fresh, float* state, float* decay, float* driven, float* conv,
+                       void* out,
                        int out_type, int tokens, int entries, int channels, int blocks, int taps_count,
                        float sharpness, cudaStream_t stream) {
     if (tokens <= 0 || entries <= 0) return 0;
@@ -186,7 +252,7 @@ ME_EXPORT int me_rglru(const float* proj, int splits, long long split_stride, co
     const size_t smem = static_cast<size_t>(GATE_TOKENS) * width * sizeof(float);
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
     RecurrentArgs a{proj, splits, (size_t)split_stride, in_bias, taps, conv_bias, ra_t, ra_bias, ri_t, ri_bias, lam,
-                    entry_of_token, cu_tokens, state_slots, fresh, state, decay, driven, out, tokens, entries, channels,
+                    entry_of_token, cu_tokens, state_slots, fresh, state, decay, driven, conv, out, tokens, entries, channels,
                     blocks, taps_count, sharpness};
     if (smem > 48 * 1024) {
         const int status = g_gates_opt_in(rglru_gates_kernel, static_cast<int>(smem));
@@ -194,9 +260,13 @@ ME_EXPORT int me_rglru(const float* proj, int splits, long long split_stride, co
     }
     const int chunks = (width + GATE_THREADS - 1) / GATE_THREADS;
     const dim3 gate_grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks * chunks);
-    int status = launch_kernel(rglru_gates_kernel, gate_grid, GATE_THREADS, smem, stream, a);
+    const size_t elements = static_cast<size_t>(tokens) * channels;
+    const int conv_blocks = static_cast<int>(std::min<size_t>((elements + 255) / 256, 148 * 32));
+    int status = launch_kernel(rglru_conv_kernel, conv_blocks, 256, 0, stream, a);
     if (status) return status;
-    const dim3 scan_grid((channels + SCAN_THREADS - 1) / SCAN_THREADS, entries);
-    if (out_type == ME_BF16) return launch_kernel(rglru_scan_kernel<__nv_bfloat16>, scan_grid, SCAN_THREADS, 0, stream, a);
-    return launch_kernel(rglru_scan_kernel<float>, scan_grid, SCAN_THREADS, 0, stream, a);
+    status = launch_kernel(rglru_gates_kernel, gate_grid, GATE_THREADS, smem, stream, a);
+    if (status) return status;
+    const dim3 scan_grid((channels + 31) / 32, entries);
+    if (out_type == ME_BF16) return launch_kernel(rglru_scan_kernel<__nv_bfloat16>, scan_grid, SCAN_WARPS * 32, 0, stream, a);
+    return launch_kernel(rglru_scan_kernel<float>, scan_grid, SCAN_WARPS * 32, 0, stream, a);
 }

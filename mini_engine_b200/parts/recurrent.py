@@ -99,6 +99,10 @@ class GatedLinearRecurrence(Mixer):
         proj = self.proj.forward(h, ctx, "recurrence.proj")
         decay = ctx.buffer("recurrence.decay", (tokens, self.channels), torch.float32)
         driven = ctx.buffer("recurrence.driven", (tokens, self.channels), torch.float32)
+        conv = ctx.buffer("recurrence.conv", (tokens, self.channels), torch.float32)
         out = ctx.buffer("recurrence.out", (tokens, self.channels), ctx.dtype)
-        ops.rglru(proj=proj, **self.held, ctx=ctx, state=cache.state, decay=decay, driven=driven, out=out, sharpness=self.sharpness)
+        ops.rglru(
+            proj=proj, **self.held, ctx=ctx, state=cache.state, decay=decay, driven=driven, conv=conv, out=out,
+            sharpness=self.sharpness,
+        )  # fmt: skip
         return self.out.forward(out, ctx, "recurrence.o")

@@ -514,7 +514,7 @@ def run_recurrence(h, w, B, entries, state, splits=2):
         proj=proj, in_bias=f(torch.cat((w["y.b"], w["x.b"]))), taps=f(w["conv"]), conv_bias=f(w["conv.b"]),
         ra_t=f(w["ra"].transpose(1, 2)), ra_bias=f(w["ra.b"].reshape(-1)), ri_t=f(w["ri"].transpose(1, 2)),
         ri_bias=f(w["ri.b"].reshape(-1)), lam=f(w["lam"]), ctx=ctx, state=state, decay=torch.empty(T, C, device="cuda"),
-        driven=torch.empty(T, C, device="cuda"), out=out, sharpness=8.0,
+        driven=torch.empty(T, C, device="cuda"), conv=torch.empty(T, C, device="cuda"), out=out, sharpness=8.0,
     )  # fmt: skip
     torch.cuda.synchronize()
     return out.cpu()
