@@ -65,6 +65,14 @@ struct GemmParams {
     int token_tiles, full_tiles, tail_parts;  // pair kernels: tiles along the tokens; whole ones; cuts of the rest
     int items;  // persistent pair kernel: whole tiles + parts of cut tiles
     int feature_tiles, group;  // persistent pair kernel: tiles along the features; token tiles of a group (see pair_item)
+    // Grouped product (lone-CTA kernel): the weight holds `group_rows` rows per group, one group after the other, and
+    // every run of `group_pad` token rows belongs to one group, `group_of_block[run]` (negative: the run holds no
+    // rows and its tiles return at once).  `outs` then counts the output features of one group.
+    const int* group_of_block = nullptr;
+    int group_pad = 0, group_rows = 0;
+    // The gated epilogue: g * sigmoid(slope * g) * (u + offset) with g = min(gate, limit), u = clamp(up, +-limit)
+    // when limit > 0.  The defaults are SwiGLU.
+    float act_slope = 1.0f, act_limit = 0.0f, act_offset = 0.0f;
 };
 
 template <int BLOCK_T, bool DUAL>
@@ -82,6 +90,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // Token tiles vary fastest in the grid: CTAs that run at the same time share a weight tile,
     // which then comes from DRAM once and from L2 for the others.
     const int n0 = blockIdx.y * BLOCK_N, t0 = blockIdx.x * BLOCK_T, split = blockIdx.z;
+    int w0 = n0;  // first weight row of the tile
+    if (p.group_of_block != nullptr) {
+        pdl_wait();  // the groups of the rows were written by a kernel before this one
+        const int group = p.group_of_block[t0 / p.group_pad];
+        if (group < 0) return;  // the whole CTA: nothing has been set up yet
+        w0 = group * p.group_rows + n0;
+    }
     const int kb_begin = split * p.k_blocks_per_split;
     const int kb_end = min(kb_begin + p.k_blocks_per_split, p.k_blocks);
     const int iterations = kb_end - kb_begin;
@@ -108,8 +123,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
                 mbar_expect_tx(&full[i], C::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                tma_load_2d(a_tile, &map_w, k, n0, &full[i]);
-                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + n0, &full[i]);
+                tma_load_2d(a_tile, &map_w, k, w0, &full[i]);
+                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + w0, &full[i]);
             }
             pdl_wait();
             for (int i = 0; i < early; ++i)
@@ -123,8 +138,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* b_tile = a_tile + C::A_BYTES;
                 mbar_expect_tx(&full[stage], C::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                tma_load_2d(a_tile, &map_w, k, n0, &full[stage]);
-                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d(a_tile, &map_w, k, w0, &full[stage]);
+                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + w0, &full[stage]);
                 tma_load_2d(b_tile, &map_x, k, t0, &full[stage]);
             }
             // Copies still in flight must land before the CTA's shared memory is released.  On
@@ -203,8 +218,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             if (t < p.tokens) {
                                 // The result is rounded to bfloat16, so the fast exponential and
                                 // division (a few ulp of float32) cost no accuracy here.
-                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
-                                out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
+                                float g = gate[c], u = up[c];
+                                if (p.act_limit > 0.0f) {
+                                    g = fminf(g, p.act_limit);
+                                    u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+                                }
+                                const float activated = __fdividef(g, 1.0f + __expf(-p.act_slope * g));
+                                out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * (u + p.act_offset));
                             }
                         }
                     }
@@ -857,6 +877,27 @@ ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, 
     }
 }
 
+
+// Grouped product over rows that are sorted by group (see GemmParams): out[t][n] = x[t] . w[group(t) * group_rows + n]
+// for n < outs, float32 [rows][outs]; or, with dual_row_offset > 0, the gated unit of rows n and dual_row_offset + n
+// of the row's group, bfloat16 [rows][outs].  `group_pad` must be a multiple of the token tile (128).
+ME_EXPORT int me_gemm_tcgen05_grouped(const void* map_w, const void* map_x, void* out, int rows, int outs, int inner,
+                                      const int* group_of_block, int group_pad, int group_rows, int dual_row_offset,
+                                      float slope, float limit, float offset, cudaStream_t stream) {
+    if (rows <= 0 || outs <= 0) return 0;
+    if (group_of_block == nullptr || group_pad < 128 || group_pad % 128 || rows % group_pad || group_rows < outs)
+        return ME_ERR_ARGUMENT;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{out, rows, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
+    p.k_blocks_per_split = p.k_blocks;
+    p.group_of_block = group_of_block;
+    p.group_pad = group_pad;
+    p.group_rows = group_rows;
+    p.act_slope = slope, p.act_limit = limit, p.act_offset = offset;
+    return dual_row_offset > 0 ? launch<128, true>(w, x, p, 1, stream) : launch<128, false>(w, x, p, 1, stream);
+}
 
 template <bool DUAL>
 static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream, int splits = 1) {

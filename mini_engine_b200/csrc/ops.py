@@ -744,6 +744,49 @@ def route(
     _check(code, "route")
 
 
+def sort_by_unit(*, chosen: torch.Tensor, units: int, pad: int, row_of: torch.Tensor, token_of: torch.Tensor,
+                 unit_of_block: torch.Tensor) -> None:  # fmt: skip
+    """Rows sorted by unit for grouped products: every (token, choice) of ``chosen [T, top]`` gets a row, each unit's
+    run padded to a multiple of ``pad``.  ``row_of [T, top]``, ``token_of [capacity]`` (-1: no token) and
+    ``unit_of_block [capacity / pad]`` (-1: no rows) are int32 outputs; ``capacity >= T * top + units * (pad - 1)``."""
+    for name, t in (("chosen", chosen), ("row_of", row_of), ("token_of", token_of), ("unit_of_block", unit_of_block)):
+        _need(t, torch.int32, name)
+    tokens, top = chosen.shape
+    capacity = token_of.shape[0]
+    if row_of.shape != chosen.shape or capacity % pad or unit_of_block.shape[0] < capacity // pad:
+        raise KernelError("sort_by_unit: shapes do not fit")
+    fn = _fn("routing", "me_sort_by_unit", [c_void_p] + [c_int] * 5 + [c_void_p] * 4)
+    code = fn(_ptr(chosen), tokens, top, int(units), int(pad), capacity, _ptr(row_of), _ptr(token_of), _ptr(unit_of_block), _stream())
+    _check(code, "sort_by_unit")
+
+
+def gather_rows(h: torch.Tensor, token_of: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[r] = h[token_of[r]]``, zeros where ``token_of[r] < 0``; rows of a multiple of 16 bytes."""
+    _need(h, None, "h"), _need(out, h.dtype, "out"), _need(token_of, torch.int32, "token_of")
+    if out.shape != (token_of.shape[0], h.shape[1]):
+        raise KernelError("gather_rows: shapes do not fit")
+    fn = _fn("routing", "me_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(h), _ptr(token_of), _ptr(out), out.shape[0], h.shape[1] * h.element_size(), _stream()), "gather_rows")
+
+
+def combine_rows(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t] = sum_k weight[t, k] * sorted_out[row_of[t, k]]`` in the order of ``k``, float32."""
+    _need(sorted_out, torch.float32, "sorted_out"), _need(row_of, torch.int32, "row_of")
+    _need(weight, torch.float32, "weight"), _need(out, torch.float32, "out")
+    tokens, top = row_of.shape
+    if weight.shape != row_of.shape or out.shape != (tokens, sorted_out.shape[1]):
+        raise KernelError("combine_rows: shapes do not fit")
+    fn = _fn("routing", "me_combine_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+    _check(fn(_ptr(sorted_out), _ptr(row_of), _ptr(weight), _ptr(out), tokens, top, out.shape[1], _stream()), "combine_rows")
+
+
+def gemm_tensor_core_grouped(plan, x, out, group_of_block, group_rows, outs, dual_rows=0, slope=1.0, limit=None, offset=0.0) -> None:
+    tensor_core.gemm_grouped(plan, x, out, group_of_block, group_rows, outs, dual_rows, slope, limit, offset)
+
+
+GROUP_PAD = 128  # rows of a run of sorted rows (tensor_core.GROUP_PAD)
+
+
 # --------------------------------------------------------------------------------- sampling
 
 

@@ -98,3 +98,109 @@ ME_EXPORT int me_route(const void* h, int h_type, const float* router, float* we
     if (h_type == ME_BF16) return launch_kernel(route_kernel<__nv_bfloat16>, tokens, ROUTE_WARPS * 32, 0, stream, a);
     return launch_kernel(route_kernel<float>, tokens, ROUTE_WARPS * 32, 0, stream, a);
 }
+
+// ------------------------------------------------------------- rows sorted by unit, for grouped products
+
+// From the lists `chosen [T][top]`: every (token, choice) gets a row in an array that is sorted by unit, each unit's
+// run padded to a multiple of `pad` rows.  Leaves `row_of [T * top]` (the row of each choice), `token_of [capacity]`
+// (the token of each row, -1 for padding and for the unused tail) and `unit_of_block [capacity / pad]` (the unit of
+// every run of `pad` rows, -1 where no rows are).  One CTA; the order of a unit's rows among themselves is not
+// fixed, and nothing depends on it: a row's products do not depend on its place.
+constexpr int SORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_by_unit_kernel(const int* __restrict__ chosen, int items, int units, int pad,
+                                                                    int capacity, int* __restrict__ row_of,
+                                                                    int* __restrict__ token_of, int* __restrict__ unit_of_block,
+                                                                    int top) {
+    __shared__ int count[MAX_UNITS], first[MAX_UNITS];
+    pdl_trigger();
+    pdl_wait();
+    for (int u = threadIdx.x; u < units; u += SORT_THREADS) count[u] = 0;
+    for (int r = threadIdx.x; r < capacity; r += SORT_THREADS) token_of[r] = -1;
+    for (int b = threadIdx.x; b < capacity / pad; b += SORT_THREADS) unit_of_block[b] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < items; i += SORT_THREADS) {
+        const int u = chosen[i];
+        if (u >= 0) atomicAdd(&count[u], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0;
+        for (int u = 0; u < units; ++u) {
+            first[u] = row;
+            const int blocks = (count[u] + pad - 1) / pad;
+            for (int b = 0; b < blocks; ++b) unit_of_block[row / pad + b] = u;
+            row += blocks * pad;
+            count[u] = 0;  // becomes the cursor of the unit's run
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < items; i += SORT_THREADS) {
+        const int u = chosen[i];
+        if (u < 0) { row_of[i] = -1; continue; }
+        const int row = first[u] + atomicAdd(&count[u], 1);
+        row_of[i] = row;
+        token_of[row] = i / top;
+    }
+}
+
+// sorted[row] = h[token_of[row]] (zeros for rows without a token), 16 bytes per thread and step.
+__global__ void gather_rows_kernel(const uint4* __restrict__ h, const int* __restrict__ token_of, uint4* __restrict__ sorted,
+                                   int rows, int chunks) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = static_cast<size_t>(rows) * chunks;
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(idx / chunks), chunk = static_cast<int>(idx % chunks);
+        const int token = token_of[row];
+        sorted[idx] = token >= 0 ? h[static_cast<size_t>(token) * chunks + chunk] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// out[t] = sum over the token's choices, in their order, of weight[t][k] * sorted_out[row_of[t][k]], float32.
+__global__ void combine_rows_kernel(const float* __restrict__ sorted_out, const int* __restrict__ row_of,
+                                    const float* __restrict__ weight, float* __restrict__ out, int tokens, int top, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = static_cast<size_t>(tokens) * width;
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(idx / width), c = static_cast<int>(idx % width);
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int row = row_of[t * top + k];
+            if (row >= 0) sum = fmaf(weight[t * top + k], sorted_out[static_cast<size_t>(row) * width + c], sum);
+        }
+        out[idx] = sum;
+    }
+}
+
+ME_EXPORT int me_sort_by_unit(const int* chosen, int tokens, int top, int units, int pad, int capacity, int* row_of,
+                              int* token_of, int* unit_of_block, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (units < 1 || units > MAX_UNITS || pad < 1 || capacity % pad) return ME_ERR_ARGUMENT;
+    // every unit's run may end in a partly filled block
+    if (static_cast<long long>(capacity) < static_cast<long long>(tokens) * top + static_cast<long long>(units) * (pad - 1))
+        return ME_ERR_ARGUMENT;
+    return launch_kernel(sort_by_unit_kernel, 1, SORT_THREADS, 0, stream, chosen, tokens * top, units, pad, capacity, row_of,
+                         token_of, unit_of_block, top);
+}
+
+ME_EXPORT int me_gather_rows(const void* h, const int* token_of, void* sorted, int rows, int row_bytes, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (row_bytes % 16 || reinterpret_cast<uintptr_t>(h) % 16 || reinterpret_cast<uintptr_t>(sorted) % 16) return ME_ERR_ARGUMENT;
+    const int chunks = row_bytes / 16;
+    const size_t total = static_cast<size_t>(rows) * chunks;
+    const int blocks = static_cast<int>((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    return launch_kernel(gather_rows_kernel, blocks, 256, 0, stream, static_cast<const uint4*>(h), token_of,
+                         static_cast<uint4*>(sorted), rows, chunks);
+}
+
+ME_EXPORT int me_combine_rows(const float* sorted_out, const int* row_of, const float* weight, float* out, int tokens, int top,
+                              int width, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const size_t total = static_cast<size_t>(tokens) * width;
+    const int blocks = static_cast<int>((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    return launch_kernel(combine_rows_kernel, blocks, 256, 0, stream, sorted_out, row_of, weight, out, tokens, top, width);
+}

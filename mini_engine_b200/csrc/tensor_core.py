@@ -68,6 +68,9 @@ def _library():
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
         lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
+        lib.me_gemm_tcgen05_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                                                ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p]
+        lib.me_gemm_tcgen05_grouped.restype = c_int
         lib.me_gemm_wait_probe.argtypes = [c_int, c_void_p, c_void_p]
         lib.me_gemm_wait_probe.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
@@ -208,6 +211,34 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int 
     _count_launch()
     if code != 0:
         raise RuntimeError(f"gated tensor-core product failed to launch (code {code})")
+
+
+GROUP_PAD = 128  # rows of a run of the sorted rows that belongs to one group: the token tile of the grouped product
+
+
+def gemm_grouped(
+    plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, group_of_block: torch.Tensor, group_rows: int, outs: int,
+    dual_rows: int = 0, slope: float = 1.0, limit: float | None = None, offset: float = 0.0,
+) -> None:  # fmt: skip
+    """A product over rows that are sorted by group: the plan's weight holds ``group_rows`` rows per group, run
+    ``b`` of ``GROUP_PAD`` rows of ``x`` belongs to group ``group_of_block[b]`` (int32 on the device; negative: no
+    rows there).  ``out [rows, outs]`` float32 is ``x[t] . w[group * group_rows + n]``; with ``dual_rows`` it is
+    bfloat16 and holds the gated unit of rows ``n`` and ``dual_rows + n`` of the row's group with the constants of
+    :func:`ops.swiglu`."""
+    _check_x(plan, x)
+    rows = x.shape[0]
+    want = torch.bfloat16 if dual_rows else torch.float32
+    if out.dtype != want or tuple(out.shape) != (rows, outs) or not out.is_contiguous():
+        raise RuntimeError(f"output {tuple(out.shape)} {out.dtype} does not fit [{rows}, {outs}] {want}")
+    if rows % GROUP_PAD or group_of_block.dtype != torch.int32 or group_of_block.numel() < rows // GROUP_PAD:
+        raise RuntimeError("the rows of a grouped product come in runs of GROUP_PAD with one int32 group each")
+    code = _library().me_gemm_tcgen05_grouped(
+        plan.map, _activation_map(x, GROUP_PAD), out.data_ptr(), rows, outs, plan.inner, group_of_block.data_ptr(),
+        GROUP_PAD, group_rows, dual_rows, float(slope), float(limit or 0.0), float(offset), _ops_stream(),
+    )  # fmt: skip
+    _count_launch()
+    if code != 0:
+        raise RuntimeError(f"grouped tensor-core product failed to launch (code {code})")
 
 
 def _count_launch() -> None:

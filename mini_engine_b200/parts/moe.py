@@ -7,13 +7,19 @@ weight_scale``.  Unit ``e``: ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -
 sigmoid(gate_slope * g) * (u + up_offset))`` (the constants of :mod:`~mini_engine_b200.parts.mlp`).  The output is
 the weighted sum of the chosen units' outputs.
 
-How it runs: all units' gate and up matrices are one row-concatenated weight and all down matrices one
-column-concatenated weight.  A routing kernel leaves a dense map ``[T, units]`` of weights (zero for units that a
-token did not choose); the activation kernel multiplies every unit's features by its weight for the token; the
-down product then *is* the weighted sum over the chosen units.  The step has no shape that depends on the choice,
-so it can be captured in a graph, and a token's result does not depend on the rest of the batch.  The price is the
-arithmetic of the units that a token did not choose, which matters for prompts when ``top`` is a small part of
-``units`` (a step of few tokens reads nearly all units' weights anyway).
+How it runs, two forms; neither has a shape that depends on the choice, so both can be captured in a graph, and in
+both a token's result does not depend on the rest of the batch.
+
+* *All units, masked* (few tokens, float32, sizes that the tensor-core product does not take): all units' gate and
+  up matrices are one row-concatenated weight and all down matrices one column-concatenated weight.  The routing
+  kernel leaves a dense map ``[T, units]`` of weights (zero for units that a token did not choose); the activation
+  kernel multiplies every unit's features by its weight for the token; the down product then *is* the weighted sum
+  over the chosen units.  A step of few tokens reads nearly all units' weights anyway.
+* *Rows sorted by unit* (bfloat16 steps of ``SORTED_MIN_TOKENS`` tokens and more): every (token, choice) gets a row
+  in an array sorted by unit, each unit's run padded to whole tiles of 128 rows; the tokens' inputs are gathered
+  into it; a grouped tensor-core product whose tiles read the weights of their run's unit forms the gated
+  activations (the gate in its epilogue), a second one the down products, and a last kernel adds a token's rows
+  with their weights in the order of its choices.  Only chosen units are computed.
 """
 
 from __future__ import annotations
@@ -26,6 +32,10 @@ from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import FeedForward, StepContext, register
 from mini_engine_b200.parts.linear import Linear
 from mini_engine_b200.weights.loader import WeightSpec
+
+# From this many tokens on a bfloat16 step sorts its rows by unit and computes only chosen units.  Below, the
+# masked form's two products over all units cost less than the sorted form's five launches and padded tiles.
+SORTED_MIN_TOKENS = 256
 
 
 @register("feed_forward", "routed_experts")
@@ -66,6 +76,7 @@ class RoutedExperts(FeedForward):
         self.gate_up: Linear | None = None
         self.down: Linear | None = None
         self.router: torch.Tensor | None = None
+        self.sorted_gate_up = self.sorted_down = None  # plans of the grouped products, when the sizes allow them
 
     def _name(self, unit: int, which: str) -> str:
         return self.prefix + self.names["unit"].format(index=unit) + self.names[which]
@@ -88,6 +99,11 @@ class RoutedExperts(FeedForward):
         self.gate_up = Linear(torch.cat(gates + ups, dim=0).contiguous())  # [all gates | all ups]
         self.down = Linear(torch.cat([tensors[self._name(unit, "down")] for unit in range(self.units)], dim=1).contiguous())
         self.router = tensors[self.prefix + self.names["router"]]
+        if gates[0].dtype == torch.bfloat16 and ops.tensor_core_gemm_supports(self.inter, self.hidden) and ops.tensor_core_gemm_supports(self.hidden, self.inter):
+            # unit after unit: [gate rows; up rows] of each, and the down matrices stacked by rows
+            stacked = torch.cat([torch.cat((gate, up), dim=0) for gate, up in zip(gates, ups)], dim=0).contiguous()
+            self.sorted_gate_up = ops.GemmPlan(stacked)
+            self.sorted_down = ops.GemmPlan(torch.cat([tensors[self._name(unit, "down")] for unit in range(self.units)], dim=0).contiguous())
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         tokens = h.shape[0]
@@ -98,7 +114,31 @@ class RoutedExperts(FeedForward):
             h=h, router=self.router, weights=weights, chosen=chosen, chosen_weight=chosen_weight, top=self.top,
             group_count=self.group_count, group_keep=self.group_keep, weight_scale=self.weight_scale,
         )  # fmt: skip
+        if self.sorted_gate_up is not None and tokens >= SORTED_MIN_TOKENS:
+            return self._forward_sorted(h, ctx, chosen, chosen_weight)
         both = self.gate_up.forward(h, ctx, "routed.gate_up")
         act = ctx.buffer("routed.act", (tokens, self.units * self.inter), ctx.dtype)
         ops.swiglu(both, act, self.gate_slope, self.limit, self.up_offset, group_weight=weights)
         return self.down.forward(act, ctx, "routed.down")
+
+    def _forward_sorted(self, h: torch.Tensor, ctx: StepContext, chosen: torch.Tensor, chosen_weight: torch.Tensor) -> torch.Tensor:
+        tokens, pad = h.shape[0], ops.GROUP_PAD
+        # every unit's run may end in a partly filled tile; the capacity is a function of the step's token count alone
+        capacity = -(-(tokens * self.top + self.units * (pad - 1)) // pad) * pad
+        grow = ctx.workspace.growing
+        row_of = grow("routed.row_of", (tokens, self.top), torch.int32)
+        token_of = grow("routed.token_of", (capacity,), torch.int32)
+        unit_of_block = grow("routed.unit_of_block", (capacity // pad,), torch.int32)
+        ops.sort_by_unit(chosen=chosen, units=self.units, pad=pad, row_of=row_of, token_of=token_of, unit_of_block=unit_of_block)
+        rows = grow("routed.rows", (capacity, self.hidden), h.dtype)
+        ops.gather_rows(h, token_of, rows)
+        act = grow("routed.sorted_act", (capacity, self.inter), h.dtype)
+        ops.gemm_tensor_core_grouped(
+            self.sorted_gate_up, rows, act, unit_of_block, 2 * self.inter, self.inter, dual_rows=self.inter,
+            slope=self.gate_slope, limit=self.limit, offset=self.up_offset,
+        )  # fmt: skip
+        down = grow("routed.sorted_down", (capacity, self.hidden), torch.float32)
+        ops.gemm_tensor_core_grouped(self.sorted_down, act, down, unit_of_block, self.hidden, self.hidden)
+        out = ctx.buffer("routed.out", (tokens, self.hidden), torch.float32)
+        ops.combine_rows(down, row_of, chosen_weight, out)
+        return out.unsqueeze(0)

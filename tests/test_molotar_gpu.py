@@ -600,6 +600,64 @@ def test_router_alone(experts, top, count, keep, dtype_name):
         assert math.isclose(float(dense[t].sum()), 1.7, rel_tol=1e-5)
 
 
+@pytest.mark.parametrize("tokens,top,units,hidden,inter", [(300, 2, 8, 64, 96), (257, 3, 5, 128, 40), (1000, 1, 3, 72, 264)])
+def test_rows_sorted_by_unit_and_grouped_products_alone(tokens, top, units, hidden, inter):
+    """Every (token, choice) gets one row in its unit's padded run; the grouped products read the weights of a run's
+    unit; a token's rows come back together with its weights in the order of its choices."""
+    from mini_engine_b200.csrc import ops
+
+    g = torch.Generator().manual_seed(tokens + units)
+    pad = ops.GROUP_PAD
+    chosen = torch.stack([torch.randperm(units, generator=g)[:top] for _ in range(tokens)]).to(torch.int32)
+    chosen[: tokens // 3] = chosen[0]  # one unit with many more rows than the others, one maybe with none
+    weight = torch.rand(tokens, top, generator=g)
+    capacity = -(-(tokens * top + units * (pad - 1)) // pad) * pad
+    row_of = torch.empty(tokens, top, dtype=torch.int32, device="cuda")
+    token_of = torch.empty(capacity, dtype=torch.int32, device="cuda")
+    unit_of_block = torch.empty(capacity // pad, dtype=torch.int32, device="cuda")
+    ops.sort_by_unit(chosen=chosen.cuda(), units=units, pad=pad, row_of=row_of, token_of=token_of, unit_of_block=unit_of_block)
+    torch.cuda.synchronize()
+    rows, owner, blocks = row_of.cpu(), token_of.cpu(), unit_of_block.cpu()
+    assert len(set(rows.flatten().tolist())) == tokens * top and int(rows.min()) >= 0 and int(rows.max()) < capacity
+    for t in range(tokens):
+        for k in range(top):
+            row = int(rows[t, k])
+            assert int(owner[row]) == t and int(blocks[row // pad]) == int(chosen[t, k])
+    assert int((owner >= 0).sum()) == tokens * top
+    h = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    gathered = torch.empty(capacity, hidden, dtype=torch.bfloat16, device="cuda")
+    ops.gather_rows(h.cuda(), token_of, gathered)
+    w_gate_up = (0.2 * torch.randn(units, 2 * inter, hidden, generator=g)).to(torch.bfloat16)
+    w_down = (0.2 * torch.randn(units, hidden, inter, generator=g)).to(torch.bfloat16)
+    act = torch.empty(capacity, inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tensor_core_grouped(ops.GemmPlan(w_gate_up.reshape(-1, hidden).contiguous().cuda()), gathered, act, unit_of_block,
+                                 2 * inter, inter, dual_rows=inter, slope=1.702, limit=1.5, offset=1.0)  # fmt: skip
+    down = torch.empty(capacity, hidden, dtype=torch.float32, device="cuda")
+    ops.gemm_tensor_core_grouped(ops.GemmPlan(w_down.reshape(-1, inter).contiguous().cuda()), act, down, unit_of_block, hidden, hidden)
+    out = torch.empty(tokens, hidden, device="cuda")
+    ops.combine_rows(down, row_of, weight.cuda(), out)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    want = torch.zeros(tokens, hidden, dtype=torch.float64)
+    for t in range(tokens):
+        for k in range(top):
+            u = int(chosen[t, k])
+            both = w_gate_up[u].double() @ h[t].double()
+            gate, up = both[:inter].clamp(max=1.5), both[inter:].clamp(-1.5, 1.5)
+            unit_act = (gate * torch.sigmoid(1.702 * gate) * (up + 1.0)).to(torch.bfloat16).double()
+            assert torch.allclose(act[int(rows[t, k])].double().cpu(), unit_act, atol=2e-2, rtol=2e-2)
+            want[t] += float(weight[t, k]) * (w_down[u].double() @ unit_act)
+    assert torch.allclose(out.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+
+
+def test_a_long_prompt_takes_the_sorted_form_and_matches_plain(folders):
+    """A bfloat16 prompt of 300 tokens in one step (rows sorted by unit), the same prompt in portions of at most 64
+    tokens (all units, masked), and the plain implementation."""
+    requests = {"long": random_ids(91, 300, CONFIG_T["vocab"])}
+    replay_and_compare(folders["T"], "bfloat16", schedules.whole(requests), requests)
+    replay_and_compare(folders["T"], "bfloat16", schedules.changing_portions(requests), requests)
+
+
 def test_sum_scaled_stream_norm_written_back():
     """``x = w * rms_norm(alpha * x + sum of the partial sums)`` in place, and the same rounded for the next sublayer."""
     from mini_engine_b200.csrc import ops
