@@ -38,7 +38,8 @@ SIZES = {
 }
 TIMED = ("biased_attention", "mixed_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
          "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding", "rglru", "route",
-         "qk_wide_norm_rope_store", "pair_embedding", "round_rows")  # fmt: skip
+         "qk_wide_norm_rope_store", "pair_embedding", "round_rows", "gemm_tensor_core_grouped", "sort_by_unit", "gather_rows",
+         "combine_rows")  # fmt: skip
 UNITS, UNITS_USED, UNIT_GROUPS, UNIT_GROUPS_KEPT = 8, 2, 4, 2
 RECURRENCE_BLOCK, RECURRENCE_TAPS = 128, 4
 
@@ -171,8 +172,10 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
         unit = 3 * width * (ff // UNITS_USED)
         used = UNITS_USED * unit
         touched = UNITS * (1.0 - (1.0 - UNITS_USED / UNITS) ** BATCH) * unit
-        bound("prompt.gemm_tensor_core", (mixer + UNITS * unit) * 2, 2 * PROMPT * (mixer + used))
-        bound("decode.gemm_tensor_core", (mixer + touched) * 2, 2 * BATCH * (mixer + used))
+        for phase, tokens, nbytes in (("prompt", PROMPT, (mixer + UNITS * unit) * 2), ("decode", BATCH, (mixer + touched) * 2)):
+            nflops = 2 * tokens * (mixer + used)
+            out[f"{phase}.products"] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6,
+                                        "kernels": ("gemm_tensor_core", "gemm_tensor_core_grouped", "swiglu")}  # fmt: skip
         # the recurrence: the projections' sums in, the decay and the driven term out and in again, the gated state out
         gates = 2 * c * RECURRENCE_BLOCK
         bound("prompt.rglru", PROMPT * c * (2 * 4 + 4 * 4 + 2) + gates * 4, 2 * PROMPT * gates)
@@ -180,6 +183,7 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
         # kernel times are averaged over all layers, of which half have an attention and half a recurrence
         for name in ("prompt.paged_attention", "decode.paged_attention", "prompt.rglru", "decode.rglru"):
             out[name] = {key: value * 0.5 for key, value in out[name].items()}
+        # (the products' record counts the activation kernel of the masked form as well: Qwen3's runs in its product's epilogue)
     elif design == "qwen3":
         mixer = width * (h * d + 2 * g * d) + h * d * width
         dense = 3 * width * ff

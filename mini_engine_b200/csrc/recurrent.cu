@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) rglru_conv_kernel(RecurrentArgs a) {
 }
 
 __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs a) {
-    extern __shared__ float u_tile[];  // [GATE_TOKENS][block_width]
+    extern __shared__ __align__(16) float u_tile[];  // [block_width][GATE_TOKENS]: a channel's 16 tokens side by side
     const int width = a.channels / a.blocks;
     const int chunks = (width + GATE_THREADS - 1) / GATE_THREADS;
     const int block = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs
     for (int idx = threadIdx.x; idx < GATE_TOKENS * width; idx += GATE_THREADS) {
         const int tok = idx / width, j = idx % width;
         const int t = first_token + tok;
-        u_tile[idx] = t < a.tokens ? a.conv[static_cast<size_t>(t) * a.channels + block * width + j] : 0.0f;
+        u_tile[j * GATE_TOKENS + tok] = t < a.tokens ? a.conv[static_cast<size_t>(t) * a.channels + block * width + j] : 0.0f;
     }
     __syncthreads();
     const int k = chunk * GATE_THREADS + threadIdx.x;
@@ -112,11 +112,14 @@ __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs
 #pragma unroll 8
     for (int j = 0; j < width; ++j) {
         const float r_weight = wr[static_cast<size_t>(j) * width], i_weight = wi[static_cast<size_t>(j) * width];
+        const float4* u4 = reinterpret_cast<const float4*>(u_tile + j * GATE_TOKENS);
 #pragma unroll
-        for (int tok = 0; tok < GATE_TOKENS; ++tok) {
-            const float u = u_tile[tok * width + j];
-            r[tok] = fmaf(r_weight, u, r[tok]);
-            g[tok] = fmaf(i_weight, u, g[tok]);
+        for (int q = 0; q < GATE_TOKENS / 4; ++q) {
+            const float4 u = u4[q];  // the same address for all lanes: one broadcast read of four tokens
+            r[4 * q] = fmaf(r_weight, u.x, r[4 * q]), g[4 * q] = fmaf(i_weight, u.x, g[4 * q]);
+            r[4 * q + 1] = fmaf(r_weight, u.y, r[4 * q + 1]), g[4 * q + 1] = fmaf(i_weight, u.y, g[4 * q + 1]);
+            r[4 * q + 2] = fmaf(r_weight, u.z, r[4 * q + 2]), g[4 * q + 2] = fmaf(i_weight, u.z, g[4 * q + 2]);
+            r[4 * q + 3] = fmaf(r_weight, u.w, r[4 * q + 3]), g[4 * q + 3] = fmaf(i_weight, u.w, g[4 * q + 3]);
         }
     }
     const float lam = a.lam[c];
@@ -129,7 +132,7 @@ __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs
         const float log_a = rate * recur;
         const size_t at = static_cast<size_t>(t) * a.channels + c;
         a.decay[at] = expf(log_a);
-        a.driven[at] = sqrtf(-expm1f(2.0f * log_a)) * input * u_tile[tok * width + k];  // sqrt(1 - a^2) i u
+        a.driven[at] = sqrtf(-expm1f(2.0f * log_a)) * input * u_tile[k * GATE_TOKENS + tok];  // sqrt(1 - a^2) i u
     }
 }
 
@@ -200,10 +203,18 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_kernel(RecurrentAr
         fetch(tile_begin + SCAN_TILE);  // the next tile's loads are in flight under the serial walk
         const int n = min(SCAN_TILE, end - tile_begin);
         if (warp == 0) {
-#pragma unroll 8
-            for (int tok = 0; tok < n; ++tok) {
-                state = fmaf(s_decay[tok][lane], state, s_state[tok][lane]);
-                s_state[tok][lane] = state;
+            // eight tokens at a time: their decays and driven terms are read first, then the chain of multiply-adds runs
+            for (int tok0 = 0; tok0 < n; tok0 += 8) {
+                float decay8[8], driven8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) decay8[i] = s_decay[tok0 + i][lane], driven8[i] = s_state[tok0 + i][lane];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (tok0 + i < n) state = fmaf(decay8[i], state, driven8[i]);
+                    driven8[i] = state;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s_state[tok0 + i][lane] = driven8[i];
             }
         }
         __syncthreads();

@@ -7,11 +7,11 @@
 // weight_scale.  Ties go to the lower index.  The kernel leaves a dense map `weights [T][units]` (zero for
 // units that were not chosen), and the chosen units and their weights as lists `[T][top]`.
 //
-// One block per token: warp w forms the scores of units w, w + 4, ...; one thread then chooses.  The sums
+// One block per token: warp w forms the scores of units w, w + 8, ...; one thread then chooses.  The sums
 // run over the columns in a fixed order, so a token's choice never depends on the rest of the batch.
 #include "common.cuh"
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
 constexpr int MAX_UNITS = 1024;
 
 struct RouteArgs {
@@ -32,10 +32,26 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(RouteArgs a) {
     pdl_trigger();
     pdl_wait();
     const T* h = static_cast<const T*>(a.h) + static_cast<size_t>(token) * a.hidden;
+    // Lane l adds the products of columns 4 l .. 4 l + 3 (+ 128 j) in ascending order into four sums of its own, which
+    // are then added in a fixed order: many loads in flight, and a token's scores are the same bits in every step.
+    const bool quads = a.hidden % 4 == 0 && reinterpret_cast<uintptr_t>(a.router) % 16 == 0 && reinterpret_cast<uintptr_t>(a.h) % 8 == 0;
     for (int unit = warp; unit < a.units; unit += ROUTE_WARPS) {
         const float* w = a.router + static_cast<size_t>(unit) * a.hidden;
         float sum = 0.0f;
-        for (int i = lane; i < a.hidden; i += 32) sum = fmaf(to_float(h[i]), w[i], sum);
+        if (quads) {
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int i = lane * 4; i < a.hidden; i += 128) {
+                const float4 weight = *reinterpret_cast<const float4*>(w + i);
+                part[0] = fmaf(to_float(h[i]), weight.x, part[0]);
+                part[1] = fmaf(to_float(h[i + 1]), weight.y, part[1]);
+                part[2] = fmaf(to_float(h[i + 2]), weight.z, part[2]);
+                part[3] = fmaf(to_float(h[i + 3]), weight.w, part[3]);
+            }
+            sum = (part[0] + part[1]) + (part[2] + part[3]);
+        } else {
+            for (int i = lane; i < a.hidden; i += 32) sum = fmaf(to_float(h[i]), w[i], sum);
+        }
         sum = warp_sum(sum);
         if (lane == 0) score[unit] = 1.0f / (1.0f + expf(-sum));
     }
