@@ -27,8 +27,9 @@
 
 constexpr int GATE_TOKENS = 16;
 constexpr int GATE_THREADS = 64;
-constexpr int SCAN_WARPS = 8;   // warps of a scan CTA: all fetch, one walks
-constexpr int SCAN_TILE = 64;   // tokens that a scan CTA holds in shared memory at a time
+constexpr int SCAN_WARPS = 16;  // warps of a scan CTA: all fetch, one walks
+constexpr int SCAN_TILE = 128;  // tokens that a scan CTA holds in shared memory at a time
+constexpr int SCAN_SMEM = 3 * SCAN_TILE * 32 * static_cast<int>(sizeof(float));
 constexpr int MAX_TAPS = 16;
 
 struct RecurrentArgs {
@@ -140,12 +141,15 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// A CTA owns 32 channels of one entry.  Its eight warps fetch a tile of 64 tokens (decay, driven term, gate
+// A CTA owns 32 channels of one entry.  Its sixteen warps fetch a tile of 128 tokens (decay, driven term, gate
 // branch) while the tile before is being worked on, and apply the gate's activation; warp 0 alone then walks the
 // tile in order, one channel per lane, which is all that is serial: one multiply-add per token.
 template <typename OutT>
 __global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_kernel(RecurrentArgs a) {
-    __shared__ float s_decay[SCAN_TILE][32], s_state[SCAN_TILE][32], s_gate[SCAN_TILE][32];
+    extern __shared__ float scan_tiles[];
+    float (*s_decay)[32] = reinterpret_cast<float (*)[32]>(scan_tiles);
+    float (*s_state)[32] = s_decay + SCAN_TILE;
+    float (*s_gate)[32] = s_state + SCAN_TILE;
     constexpr int PER_THREAD = SCAN_TILE / SCAN_WARPS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * 32 + lane;
@@ -278,6 +282,12 @@ ME_EXPORT int me_rglru(const float* proj, int splits, long long split_stride, co
     status = launch_kernel(rglru_gates_kernel, gate_grid, GATE_THREADS, smem, stream, a);
     if (status) return status;
     const dim3 scan_grid((channels + 31) / 32, entries);
-    if (out_type == ME_BF16) return launch_kernel(rglru_scan_kernel<__nv_bfloat16>, scan_grid, SCAN_WARPS * 32, 0, stream, a);
-    return launch_kernel(rglru_scan_kernel<float>, scan_grid, SCAN_WARPS * 32, 0, stream, a);
+    if (out_type == ME_BF16) {
+        static SharedMemoryOptIn opt_in;
+        if (const int e = opt_in(rglru_scan_kernel<__nv_bfloat16>, SCAN_SMEM)) return e;
+        return launch_kernel(rglru_scan_kernel<__nv_bfloat16>, scan_grid, SCAN_WARPS * 32, SCAN_SMEM, stream, a);
+    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(rglru_scan_kernel<float>, SCAN_SMEM)) return e;
+    return launch_kernel(rglru_scan_kernel<float>, scan_grid, SCAN_WARPS * 32, SCAN_SMEM, stream, a);
 }
