@@ -63,11 +63,11 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(RouteArgs a) {
     if (threadIdx.x != 0) return;
     const int per = a.units / a.group_count;
     // The best groups, one at a time (group counts are small).
-    for (int round = 0; round < a.group_keep; ++round) {
+    for (int turn = 0; turn < a.group_keep; ++turn) {
         int best = -1;
         float best_value = -INFINITY;
         for (int g = 0; g < a.group_count; ++g) {
-            if (eligible[g * per]) continue;  // taken in an earlier round
+            if (eligible[g * per]) continue;  // taken in an earlier turn
             float first = -INFINITY, second = -INFINITY;
             for (int u = g * per; u < (g + 1) * per; ++u) {
                 const float s = score[u];
@@ -83,21 +83,21 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(RouteArgs a) {
     float total = 0.0f;
     int* chosen = a.chosen + static_cast<size_t>(token) * a.top;
     float* chosen_weight = a.chosen_weight + static_cast<size_t>(token) * a.top;
-    for (int round = 0; round < a.top; ++round) {
+    for (int turn = 0; turn < a.top; ++turn) {
         int best = -1;
         float best_score = -INFINITY;
         for (int u = 0; u < a.units; ++u)
             if (eligible[u] == 1 && score[u] > best_score) best_score = score[u], best = u;
-        chosen[round] = best;
+        chosen[turn] = best;
         if (best < 0) continue;
         eligible[best] = 2;
         total += best_score;
     }
     const float inv = a.weight_scale / (total + 1e-20f);
-    for (int round = 0; round < a.top; ++round) {
-        const int u = chosen[round];
+    for (int turn = 0; turn < a.top; ++turn) {
+        const int u = chosen[turn];
         const float weight = u >= 0 ? score[u] * inv : 0.0f;
-        chosen_weight[round] = weight;
+        chosen_weight[turn] = weight;
         if (u >= 0) a.weights[static_cast<size_t>(token) * a.units + u] = weight;
     }
 }
