@@ -744,3 +744,44 @@ def test_greedy_generation_through_the_engine(folders, dtype_name, name):
             assert float(row.max() - row[token]) <= slack, f"token {i} of a {len(prompt)}-token prompt"
     again = engine.generate(prompts[:2], SamplingParams(max_tokens=24, ignore_eos=True))
     assert again == got[:2]  # slots and pages of finished requests serve new ones
+
+
+def test_the_command_line_and_sampling_with_temperature(folders, capsys):
+    """`python -m mini_engine_b200.cli.generate` on a folder of this design: greedy output equals the engine's, and a
+    run with temperature draws tokens of the vocabulary through the device sampler."""
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.cli import generate
+
+    folder = str(folders["S"])
+    prompts = [random_ids(70 + i, n, CONFIG_S["vocab"]) for i, n in enumerate((12, 30))]
+    ids = ";".join(",".join(map(str, p)) for p in prompts)
+    common = ["--model", folder, "--dtype", "fp32", "--max-tokens", "6", "--ignore-eos", "--num-blocks", "32", "--max-model-len", "128",
+              "--max-num-seqs", "2", "--prompt-ids", ids]  # fmt: skip
+    assert generate.main(common) == 0
+    greedy = capsys.readouterr().out
+    engine = LLMEngine.from_pretrained(folder, EngineConfig(block_size=16, num_blocks=32, max_model_len=128, max_num_seqs=2, dtype=torch.float32))
+    want = engine.generate(prompts[:1], SamplingParams(max_tokens=6, ignore_eos=True)) + engine.generate(prompts[1:], SamplingParams(max_tokens=6, ignore_eos=True))
+    for prompt, tokens in zip(prompts, want):
+        assert f"prompt ({len(prompt)} tokens) -> {tokens}" in greedy
+    assert generate.main(common + ["--temperature", "0.8", "--seed", "3"]) == 0
+    drawn = capsys.readouterr().out.splitlines()[:2]
+    for line, prompt in zip(drawn, prompts):
+        tokens = json.loads(line.split("-> ")[1])
+        assert line.startswith(f"prompt ({len(prompt)} tokens)") and len(tokens) == 6 and all(0 <= t < CONFIG_S["vocab"] for t in tokens)
+
+
+def test_preempted_requests_start_again_from_zero_state(folders):
+    """A pool so small that running requests are preempted: their pages and state slots go back, they are computed
+    again from their first token (the recurrent state, the convolution's history and the last token start from
+    nothing), and the tokens are those of a run with room for everyone."""
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = folders["S"]
+    prompts = [random_ids(90 + i, n, CONFIG_S["vocab"]) for i, n in enumerate((40, 33, 25, 47))]
+    params = SamplingParams(max_tokens=30, ignore_eos=True)
+    roomy = LLMEngine.from_pretrained(folder, EngineConfig(block_size=16, num_blocks=64, max_model_len=128, max_num_seqs=4, dtype=torch.float32))
+    want = roomy.generate(prompts, params)
+    tight = LLMEngine.from_pretrained(folder, EngineConfig(block_size=16, num_blocks=11, max_model_len=128, max_num_seqs=4, dtype=torch.float32))
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.num_preemptions > 0
+    assert got == want
