@@ -15,7 +15,7 @@
 // `[K][C]` floats: row 0 is S, rows 1 .. K-1 the last K-1 inputs x of the convolution, oldest first.  An entry
 // that starts its sequence starts from zeros.
 //
-// Three kernels.  `conv`: a thread per (token, channel) forms u (the convolution reaches back into the entry's
+// Three kernels.  `conv`: a thread per (token, channel), one token per grid column, forms u (the convolution reaches back into the entry's
 // earlier tokens of this step or into the state) and leaves it in scratch.  `gates`: a CTA takes 16 tokens of one
 // block, holds their u in shared memory and forms 64 channels' two gates, reading each weight once for the 16
 // tokens; it leaves a_t and the driven term in scratch.  `scan`: a CTA per
@@ -67,24 +67,22 @@ __device__ __forceinline__ float branch_input(const RecurrentArgs& a, int t, int
 
 __global__ void __launch_bounds__(256) rglru_conv_kernel(RecurrentArgs a) {
     const int K = a.taps_count;
-    const size_t total = static_cast<size_t>(a.tokens) * a.channels;
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * 256 + threadIdx.x;
     pdl_trigger();
     pdl_wait();
-    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
-         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const int t = static_cast<int>(idx / a.channels), c = static_cast<int>(idx % a.channels);
-        const int entry = a.entry_of_token[t];
-        const int n = t - a.cu_tokens[entry];  // tokens of this entry in front of t
-        const float* history = a.fresh[entry] ? nullptr : a.state + (static_cast<size_t>(a.state_slots[entry]) * K + 1) * a.channels;
-        float u = a.conv_bias[c];
-        for (int back = 0; back < K; ++back) {
-            float x = 0.0f;
-            if (n - back >= 0) x = branch_input(a, t - back, a.channels + c);
-            else if (history) x = history[static_cast<size_t>(n - back + K - 1) * a.channels + c];
-            u = fmaf(a.taps[static_cast<size_t>(c) * K + (K - 1 - back)], x, u);
-        }
-        a.conv[idx] = u;
+    if (c >= a.channels) return;
+    const int entry = a.entry_of_token[t];
+    const int n = t - a.cu_tokens[entry];  // tokens of this entry in front of t
+    const float* history = a.fresh[entry] ? nullptr : a.state + (static_cast<size_t>(a.state_slots[entry]) * K + 1) * a.channels;
+    float u = a.conv_bias[c];
+    for (int back = 0; back < K; ++back) {
+        float x = 0.0f;
+        if (n - back >= 0) x = branch_input(a, t - back, a.channels + c);
+        else if (history) x = history[static_cast<size_t>(n - back + K - 1) * a.channels + c];
+        u = fmaf(a.taps[static_cast<size_t>(c) * K + (K - 1 - back)], x, u);
     }
+    a.conv[static_cast<size_t>(t) * a.channels + c] = u;
 }
 
 __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs a) {
@@ -275,9 +273,8 @@ ME_EXPORT int me_rglru(const float* proj, int splits, long long split_stride, co
     }
     const int chunks = (width + GATE_THREADS - 1) / GATE_THREADS;
     const dim3 gate_grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks * chunks);
-    const size_t elements = static_cast<size_t>(tokens) * channels;
-    const int conv_blocks = static_cast<int>(std::min<size_t>((elements + 255) / 256, 148 * 32));
-    int status = launch_kernel(rglru_conv_kernel, conv_blocks, 256, 0, stream, a);
+    const dim3 conv_grid(tokens, (channels + 255) / 256);
+    int status = launch_kernel(rglru_conv_kernel, conv_grid, 256, 0, stream, a);
     if (status) return status;
     status = launch_kernel(rglru_gates_kernel, gate_grid, GATE_THREADS, smem, stream, a);
     if (status) return status;

@@ -15,7 +15,8 @@ both a token's result does not depend on the rest of the batch.
   kernel leaves a dense map ``[T, units]`` of weights (zero for units that a token did not choose); the activation
   kernel multiplies every unit's features by its weight for the token; the down product then *is* the weighted sum
   over the chosen units.  A step of few tokens reads nearly all units' weights anyway.
-* *Rows sorted by unit* (bfloat16 steps of ``SORTED_MIN_TOKENS`` tokens and more): every (token, choice) gets a row
+* *Rows sorted by unit* (bfloat16 steps of ``SORTED_MIN_TOKENS`` tokens and more, and steps of so few tokens that
+  their choices cannot touch half of the units): every (token, choice) gets a row
   in an array sorted by unit, each unit's run padded to whole tiles of 128 rows; the tokens' inputs are gathered
   into it; a grouped tensor-core product whose tiles read the weights of their run's unit forms the gated
   activations (the gate in its epilogue), a second one the down products, and a last kernel adds a token's rows
@@ -114,7 +115,9 @@ class RoutedExperts(FeedForward):
             h=h, router=self.router, weights=weights, chosen=chosen, chosen_weight=chosen_weight, top=self.top,
             group_count=self.group_count, group_keep=self.group_keep, weight_scale=self.weight_scale,
         )  # fmt: skip
-        if self.sorted_gate_up is not None and tokens >= SORTED_MIN_TOKENS:
+        # Many tokens: only chosen units are computed.  Very few: only chosen units' weights are read.  The choice
+        # depends on the token count alone, so a captured step always takes the form it was captured with.
+        if self.sorted_gate_up is not None and (tokens >= SORTED_MIN_TOKENS or 2 * tokens * self.top <= self.units):
             return self._forward_sorted(h, ctx, chosen, chosen_weight)
         both = self.gate_up.forward(h, ctx, "routed.gate_up")
         act = ctx.buffer("routed.act", (tokens, self.units * self.inter), ctx.dtype)
