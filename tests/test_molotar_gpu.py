@@ -127,12 +127,12 @@ def expected_logits(folder, requests, routing=None):
     return out
 
 
-def replay(folder, dtype_name, steps, block_size=16, max_tokens=None, routing=None, max_live=4):
+def replay(folder, dtype_name, steps, block_size=16, max_tokens=None, routing=None, max_live=4, max_step_tokens=512):
     """``routing`` (a dict) is filled with what the routed feed-forwards chose: request -> feed-forward -> position -> units."""
     from mini_engine_b200.engine.replay import Replayer
     from mini_engine_b200.parts import moe as moe_module
 
-    replayer = Replayer(folder, DTYPES[dtype_name], max_tokens or schedules.peak_live_tokens(steps), block_size, max_step_tokens=512, max_live=max_live)
+    replayer = Replayer(folder, DTYPES[dtype_name], max_tokens or schedules.peak_live_tokens(steps), block_size, max_step_tokens=max_step_tokens, max_live=max_live)
     calls: list = []
     original = moe_module.RoutedExperts.forward
 
@@ -200,6 +200,38 @@ def test_schedules_match_plain(name, dtype_name, schedule, folders):
     requests = requests_for(name)
     steps = getattr(schedules, schedule)(requests)
     replay_and_compare(folders[name], dtype_name, steps, requests)
+
+
+UNUSUAL = {
+    # no layer keeps keys and values: no cache group at all, only state slots
+    "only_recurrences": [
+        {"type": "rglru", "mixer": {"width": 64, "blocks": 2, "conv": 4}, "mlp": routed(32, 2.0, 4, 2, 1.0, 2, 1)},
+        {"type": "rglru", "mixer": {"width": 96, "blocks": 3, "conv": 2}, "mlp": None},
+    ],
+    # the embedding's last token is the only per-request state
+    "one_attention": [{"type": "attention", "mixer": attention(2, 2, 32, 32, 0.2, 40, {"dims": 32, "base": 1000.0}), "mlp": routed(32, 2.0, 4, 2, 1.0, 2, 1)}],
+    # two readers of one owner that has no window itself: one with a window shorter than a page, one with a long one;
+    # 32 units of which a token uses 2 (a decode step reads only the chosen units' weights)
+    "readers_of_one_owner": [
+        {"type": "attention", "mixer": attention(4, 1, 64, 64, 0.125, None, None), "mlp": None},
+        {"type": "attention", "mixer": attention(4, 1, 64, 64, 0.125, 10, None, kv_from=0), "mlp": None},
+        {"type": "attention", "mixer": attention(4, 1, 64, 64, 0.3, 200, None, kv_from=0), "mlp": routed(64, 2.0, 32, 2, 1.0, 8, 2)},
+    ],
+}
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(UNUSUAL))
+def test_unusual_layer_combinations(name, dtype_name, tmp_path):
+    from mini_engine_b200.config import MolotarConfig
+    from mini_engine_b200.weights import write_random_model
+
+    raw = {"architecture": "Molotar", "vocab": 200, "width": 64, "norm": {"eps": 1e-5}, "postln_alpha": 1.5,
+           "embedding": {"scale": 8.0, "bigram": {"buckets": 97, "mul_prev": 5, "mul_cur": 3}}, "layers": UNUSUAL[name]}  # fmt: skip
+    write_random_model(tmp_path, MolotarConfig.from_dict(raw), seed=5, dtype=torch.bfloat16, scale=6.0)
+    requests = {"a": random_ids(1, 300, 200), "b": random_ids(2, 77, 200), "c": random_ids(3, 1, 200), "d": random_ids(4, 2, 200)}
+    for maker in (schedules.whole, schedules.changing_portions, schedules.mixed, lambda r: schedules.tail_one_by_one(r, 32)):
+        replay_and_compare(tmp_path, dtype_name, maker(requests), requests)
 
 
 @pytest.mark.parametrize("block_size", [4, 16, 32])
