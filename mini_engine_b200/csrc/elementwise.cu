@@ -1,6 +1,7 @@
-// Memory-bound kernels between the matrix products: embedding lookup, residual sum fused
-// with RMSNorm, the SwiGLU gate on partial sums, and per-head q/k norm + rotary + cache
-// write.  Statistics, angles and sums are 32-bit; outputs are rounded once.
+// Memory-bound kernels between the matrix products: embedding lookup (plain, and with a second
+// table chosen by the pair of the previous and the current token), residual sum fused with RMSNorm,
+// the SwiGLU gate on partial sums, and q/k norm (per head, or over whole projections) + rotary +
+// cache write.  Statistics, angles and sums are 32-bit; outputs are rounded once.
 //
 // Formulas restate YuvGev00/mini-engine: src/mini_engine/model.py:59-69 (RMSNorm),
 // :72-90 (rotary, rotate-half), :113-116 (norm before rotation, v untouched), :130 (SwiGLU),
@@ -106,9 +107,11 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
     *reinterpret_cast<uint2*>(dst) = packed;
 }
 
-// One block per output row.  x_row = x[src] + sum_s pending[s][src] (ascending s); when
+// One block per output row.  x_row = x_scale * x[src] + sum_s pending[s][src] (ascending s); when
 // `rows` is null the sum is written back to x (the residual stream advances), otherwise only
 // the listed rows are read and x is left alone.  out = weight * x_row * rsqrt(mean(x_row^2) + eps).
+// With `keep_normed` (and no `rows`) it is the normalised row, in float32, that is written back to x
+// instead of the sum: a layer whose norm follows the sum.  x_scale is 1 in pre-norm layers (exact).
 // VEC: hidden is a multiple of 4 and every pointer is 16-byte aligned; all loads of a thread are
 // then issued before any of them is used, which is what matters when only a few rows run.
 //
@@ -286,7 +289,9 @@ ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long lo
 
 // partial[s][t][0..inter) are gate sums, [inter..2*inter) up sums.  out = g * sigmoid(slope * g) * (u + offset)
 // with g = min(gate, limit) and u = clamp(up, -limit, limit) when limit > 0, else g = gate and u = up;
-// slope 1, no limit and offset 0 are silu(gate) * up.
+// slope 1, no limit and offset 0 are silu(gate) * up.  With `group_weight [tokens][groups]` the features form
+// `groups` equal runs (the units of a routed feed-forward side by side) and feature i of token t is multiplied
+// by group_weight[t][i / group_size].
 template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                               OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset,
