@@ -130,7 +130,9 @@ __global__ void __launch_bounds__(GATE_THREADS) rglru_gates_kernel(RecurrentArgs
         const float recur = 1.0f / (1.0f + expf(-r[tok])), input = 1.0f / (1.0f + expf(-g[tok]));
         const float log_a = rate * recur;
         const size_t at = static_cast<size_t>(t) * a.channels + c;
-        a.decay[at] = expf(log_a);
+        // 1 + expm1(x) and not exp(x): near x = 0 the sum is the float nearest to the true decay, where expf may be off by
+        // two ulp in one direction, which a state that lives for a thousand tokens multiplies up token by token
+        a.decay[at] = 1.0f + expm1f(log_a);
         a.driven[at] = sqrtf(-expm1f(2.0f * log_a)) * input * u_tile[k * GATE_TOKENS + tok];  // sqrt(1 - a^2) i u
     }
 }
